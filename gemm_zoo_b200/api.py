@@ -1,0 +1,265 @@
+"""ctypes binding of include/gemmzoo/gemm.h, plus ``Sm100Gemm``, a Python mirror
+of the reference functor concept (constructed from the problem, then called
+with operands, scalars and a stream; nvidia/kernel_functors/bf16_mma_gemm.cuh:17-18,51-52).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+
+# enums (mirror gemm.h)
+DT_F16, DT_BF16, DT_F32, DT_S8, DT_S32 = 0, 1, 2, 3, 4
+ROW_MAJOR, COL_MAJOR = 0, 1
+CFG_AUTO, CFG_1CTA_N256, CFG_1CTA_N128, CFG_1CTA_N64, CFG_2CTA_N256, CFG_2CTA_N128, CFG_SIMT = 0, 1, 2, 3, 4, 5, 15
+FLAG_EPILOGUE_DIRECT, FLAG_EPILOGUE_TMA, FLAG_TEST_WITHHOLD_ACC_READY = 0x1, 0x2, 0x80000000
+
+GZ_OK = 0
+GZ_ERR_INVALID_ARG, GZ_ERR_UNSUPPORTED, GZ_ERR_MISALIGNED, GZ_ERR_CUDA = 1, 2, 3, 4
+GZ_ERR_DEVICE_TIMEOUT, GZ_ERR_NO_DEVICE, GZ_ERR_TOO_LARGE, GZ_ERR_OUT_OF_MEMORY = 5, 6, 7, 8
+
+# Every symbol include/gemmzoo/gemm.h declares.
+EXPORTED_SYMBOLS = [
+    "gz_gemm_desc_validate", "gz_gemm_plan_create", "gz_gemm_plan_destroy", "gz_gemm_plan_info",
+    "gz_gemm_run", "gz_gemm_run_host", "gz_last_device_status", "gz_status_string",
+    "gz_last_cuda_error", "gz_fill", "gz_tile_coords", "gz_partition_columns", "gz_version",
+]
+
+
+class GemmDesc(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("in_type", C.c_int32), ("out_type", C.c_int32),
+        ("layout_a", C.c_int32), ("layout_b", C.c_int32), ("device", C.c_int32),
+        ("config", C.c_int32), ("flags", C.c_uint32),
+        ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
+        ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64), ("ldd", C.c_int64),
+        ("wait_limit_ns", C.c_uint64),
+    ]
+
+    @classmethod
+    def make(cls, in_type, out_type, m, n, k, layout_a=ROW_MAJOR, layout_b=ROW_MAJOR, lda=0, ldb=0,
+             ldc=0, ldd=0, device=0, config=CFG_AUTO, flags=0, wait_limit_ns=0):
+        d = cls()
+        d.struct_size = C.sizeof(cls)
+        d.in_type, d.out_type = in_type, out_type
+        d.layout_a, d.layout_b = layout_a, layout_b
+        d.device, d.config, d.flags = device, config, flags
+        d.m, d.n, d.k = m, n, k
+        d.lda, d.ldb, d.ldc, d.ldd = lda, ldb, ldc, ldd
+        d.wait_limit_ns = wait_limit_ns
+        return d
+
+
+class PlanInfo(C.Structure):
+    _fields_ = [
+        ("config", C.c_int32), ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32),
+        ("stages", C.c_int32), ("ctas_per_tile", C.c_int32), ("grid", C.c_int32),
+        ("smem_bytes", C.c_int32), ("epilogue_tma", C.c_int32), ("sm_count", C.c_int32),
+        ("tiles", C.c_int64),
+        ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64), ("ldd", C.c_int64),
+    ]
+
+    def as_dict(self):
+        return {f: getattr(self, f) for f, _ in self._fields_}
+
+
+class GzError(RuntimeError):
+    def __init__(self, status, where=""):
+        self.status = status
+        msg = status_string(status)
+        if status == GZ_ERR_CUDA:
+            msg += ": " + lib().gz_last_cuda_error().decode()
+        super().__init__(f"{where}: {msg}" if where else msg)
+
+
+_lib = None
+
+
+def lib_path() -> Path:
+    return PKG / "libgemmzoo.so"
+
+
+def lib():
+    """Load libgemmzoo.so.  Raises if it has not been built: there is no fallback path."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    p = lib_path()
+    if not p.exists():
+        raise RuntimeError(f"{p} is missing; build it with `python -m gemm_zoo_b200.build lib` "
+                           "(or __graft_entry__.build())")
+    L = C.CDLL(str(p))
+    vp, i32, i64, u32, u64 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint32, C.c_uint64
+    L.gz_gemm_desc_validate.argtypes = [C.POINTER(GemmDesc), C.c_int, C.POINTER(PlanInfo)]
+    L.gz_gemm_desc_validate.restype = C.c_int
+    L.gz_gemm_plan_create.argtypes = [C.POINTER(vp), C.POINTER(GemmDesc)]
+    L.gz_gemm_plan_create.restype = C.c_int
+    L.gz_gemm_plan_destroy.argtypes = [vp]
+    L.gz_gemm_plan_destroy.restype = C.c_int
+    L.gz_gemm_plan_info.argtypes = [vp, C.POINTER(PlanInfo)]
+    L.gz_gemm_plan_info.restype = C.c_int
+    L.gz_gemm_run.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp]
+    L.gz_gemm_run.restype = C.c_int
+    L.gz_gemm_run_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp]
+    L.gz_gemm_run_host.restype = C.c_int
+    L.gz_last_device_status.argtypes = [vp, vp, C.POINTER(u32 * 4)]
+    L.gz_last_device_status.restype = C.c_int
+    L.gz_status_string.argtypes = [C.c_int]
+    L.gz_status_string.restype = C.c_char_p
+    L.gz_last_cuda_error.argtypes = []
+    L.gz_last_cuda_error.restype = C.c_char_p
+    L.gz_fill.argtypes = [vp, i32, i64, u64, u32, i32, C.c_float, vp]
+    L.gz_fill.restype = C.c_int
+    L.gz_tile_coords.argtypes = [u32, u32, u32, u32, C.POINTER(u32), C.POINTER(u32)]
+    L.gz_tile_coords.restype = None
+    L.gz_partition_columns.argtypes = [i64, i32, i32, i64, C.POINTER(i64), C.POINTER(i64)]
+    L.gz_partition_columns.restype = C.c_int
+    L.gz_version.argtypes = []
+    L.gz_version.restype = i32
+    _lib = L
+    return L
+
+
+def status_string(status: int) -> str:
+    return lib().gz_status_string(int(status)).decode()
+
+
+def validate(desc: GemmDesc, sm_count: int = 0):
+    """Host-only validation.  Returns (status, PlanInfo)."""
+    info = PlanInfo()
+    st = lib().gz_gemm_desc_validate(C.byref(desc), sm_count, C.byref(info))
+    return st, info
+
+
+def tile_coords(tiles_m, tiles_n, group_m, t):
+    tm, tn = C.c_uint32(), C.c_uint32()
+    lib().gz_tile_coords(tiles_m, tiles_n, group_m, t, C.byref(tm), C.byref(tn))
+    return tm.value, tn.value
+
+
+def partition_columns(n, parts, p, align=8):
+    b, e = C.c_int64(), C.c_int64()
+    st = lib().gz_partition_columns(n, parts, p, align, C.byref(b), C.byref(e))
+    if st != GZ_OK:
+        raise GzError(st, "gz_partition_columns")
+    return b.value, e.value
+
+
+def _scalar(in_type, v):
+    return C.c_int32(int(v)) if in_type == DT_S8 else C.c_float(float(v))
+
+
+def _ptr(x):
+    """Device/host address of a torch tensor, numpy array, int, or None."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    if hasattr(x, "ctypes"):
+        return x.ctypes.data
+    raise TypeError(type(x))
+
+
+def _stream_handle(stream):
+    if stream is None:
+        return None
+    if isinstance(stream, int):
+        return stream or None
+    return stream.cuda_stream or None  # torch.cuda.Stream
+
+
+class Plan:
+    """Owns a gz_plan."""
+
+    def __init__(self, desc: GemmDesc):
+        self.desc = desc
+        self._h = C.c_void_p()
+        st = lib().gz_gemm_plan_create(C.byref(self._h), C.byref(desc))
+        if st != GZ_OK:
+            self._h = C.c_void_p()
+            raise GzError(st, "gz_gemm_plan_create")
+
+    def info(self) -> PlanInfo:
+        info = PlanInfo()
+        st = lib().gz_gemm_plan_info(self._h, C.byref(info))
+        if st != GZ_OK:
+            raise GzError(st, "gz_gemm_plan_info")
+        return info
+
+    def run(self, a, b, c, d, alpha, beta, stream=None):
+        al, be = _scalar(self.desc.in_type, alpha), _scalar(self.desc.in_type, beta)
+        st = lib().gz_gemm_run(self._h, _ptr(a), _ptr(b), _ptr(c), _ptr(d), C.byref(al), C.byref(be),
+                               _stream_handle(stream))
+        if st != GZ_OK:
+            raise GzError(st, "gz_gemm_run")
+
+    def run_host(self, a, b, c, d, alpha, beta, stream=None):
+        al, be = _scalar(self.desc.in_type, alpha), _scalar(self.desc.in_type, beta)
+        st = lib().gz_gemm_run_host(self._h, _ptr(a), _ptr(b), _ptr(c), _ptr(d), C.byref(al),
+                                    C.byref(be), _stream_handle(stream))
+        if st != GZ_OK:
+            raise GzError(st, "gz_gemm_run_host")
+
+    def device_status(self, stream=None):
+        """(status, detail[4]) after synchronising `stream`."""
+        detail = (C.c_uint32 * 4)()
+        st = lib().gz_last_device_status(self._h, _stream_handle(stream), C.byref(detail))
+        return st, list(detail)
+
+    def destroy(self):
+        if self._h:
+            lib().gz_gemm_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+_TORCH_DT = None
+
+
+def _torch_dtype_code(t):
+    global _TORCH_DT
+    if _TORCH_DT is None:
+        import torch
+        _TORCH_DT = {torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.float32: DT_F32,
+                     torch.int8: DT_S8, torch.int32: DT_S32}
+    return _TORCH_DT[t]
+
+
+class Sm100Gemm:
+    """Mirror of the reference functor concept.
+
+    Reference: ``Kernel kernel(m, n, k, properties); kernel(a, b, c, d, alpha, beta, stream);``
+    (nvidia/utils/benchmark.cuh:54-57).  Defaults reproduce the reference
+    convention: A row-major ld=k, B row-major ld=n, C/D row-major ld=n.
+    """
+
+    def __init__(self, m, n, k, in_dtype, out_dtype, layout_a=ROW_MAJOR, layout_b=ROW_MAJOR, lda=0,
+                 ldb=0, ldc=0, ldd=0, device=0, config=CFG_AUTO, flags=0, wait_limit_ns=0):
+        it = in_dtype if isinstance(in_dtype, int) else _torch_dtype_code(in_dtype)
+        ot = out_dtype if isinstance(out_dtype, int) else _torch_dtype_code(out_dtype)
+        self.desc = GemmDesc.make(it, ot, m, n, k, layout_a, layout_b, lda, ldb, ldc, ldd, device,
+                                  config, flags, wait_limit_ns)
+        self.plan = Plan(self.desc)
+
+    def __call__(self, a, b, c, d, alpha, beta, stream=None):
+        self.plan.run(a, b, c, d, alpha, beta, stream)
+
+    def info(self):
+        return self.plan.info()
+
+
+def fill(t, seed, stream_id, dist, scale=1.0, stream=None):
+    """Seeded fill of a contiguous torch CUDA tensor (see gz_fill)."""
+    st = lib().gz_fill(t.data_ptr(), _torch_dtype_code(t.dtype), t.numel(), seed, stream_id, dist,
+                       float(scale), _stream_handle(stream))
+    if st != GZ_OK:
+        raise GzError(st, "gz_fill")
+    return t

@@ -1,0 +1,791 @@
+// C ABI of the library (see include/gemmzoo/gemm.h): descriptor validation,
+// plan creation (configuration choice, shared-memory opt-in, launch geometry),
+// per-call tensor-map encoding and launch, host-operand convenience path,
+// device status read-back, seeded fills and the column partition helper.
+//
+// The plan does what the constructor of a reference functor does
+// (nvidia/kernel_functors/bf16_mma_gemm.cuh:17-49) and gz_gemm_run does what its
+// operator() does (:51-63): one asynchronous launch, no host synchronisation.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+
+#include "gemmzoo/gemm.h"
+#include "rng.h"
+#include "simt_gemm.cuh"
+#include "sm100_gemm.cuh"
+#include "tile_sched.h"
+
+namespace {
+
+thread_local std::string g_last_cuda_error;
+
+bool cuda_ok(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return true;
+  g_last_cuda_error = std::string(what) + ": " + cudaGetErrorString(e);
+  (void)cudaGetLastError();
+  return false;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    (void)cudaGetLastError();
+  });
+  return fn;
+}
+
+int dtype_size(int dt) {
+  switch (dt) {
+    case GZ_DT_F16:
+    case GZ_DT_BF16: return 2;
+    case GZ_DT_F32:
+    case GZ_DT_S32: return 4;
+    case GZ_DT_S8: return 1;
+  }
+  return 0;
+}
+
+bool pair_supported(int in, int out) {
+  return (in == GZ_DT_F16 && (out == GZ_DT_F16 || out == GZ_DT_F32)) ||
+         (in == GZ_DT_BF16 && (out == GZ_DT_BF16 || out == GZ_DT_F32)) ||
+         (in == GZ_DT_F32 && out == GZ_DT_F32) || (in == GZ_DT_S8 && out == GZ_DT_S32);
+}
+
+struct CfgShape {
+  int config, ctas, bn, stages;
+  double eff;  // rough relative efficiency of the tile shape, for the chooser only
+};
+const CfgShape kShapes[] = {
+    {GZ_CFG_2CTA_N256, 2, 256, 6, 1.00}, {GZ_CFG_1CTA_N256, 1, 256, 4, 0.90},
+    {GZ_CFG_2CTA_N128, 2, 128, 8, 0.80}, {GZ_CFG_1CTA_N128, 1, 128, 6, 0.72},
+    {GZ_CFG_1CTA_N64, 1, 64, 8, 0.45},
+};
+const CfgShape* shape_of(int config) {
+  for (const auto& s : kShapes)
+    if (s.config == config) return &s;
+  return nullptr;
+}
+
+int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Normalised view of a descriptor.
+struct Problem {
+  gz_gemm_desc d;
+  int in_size, out_size;
+  bool a_mn_major, b_mn_major;  // A column-major / B row-major
+  bool tma_ld_ok;               // leading dimensions satisfy TMA's 16-byte stride rule
+};
+
+gz_status normalise(const gz_gemm_desc* desc, Problem* pr) {
+  if (!desc) return GZ_ERR_INVALID_ARG;
+  if (desc->struct_size != sizeof(gz_gemm_desc)) return GZ_ERR_INVALID_ARG;
+  gz_gemm_desc d = *desc;
+  if (d.m <= 0 || d.n <= 0 || d.k <= 0) return GZ_ERR_INVALID_ARG;
+  if (d.layout_a != GZ_ROW_MAJOR && d.layout_a != GZ_COL_MAJOR) return GZ_ERR_INVALID_ARG;
+  if (d.layout_b != GZ_ROW_MAJOR && d.layout_b != GZ_COL_MAJOR) return GZ_ERR_INVALID_ARG;
+  if (dtype_size(d.in_type) == 0 || dtype_size(d.out_type) == 0) return GZ_ERR_INVALID_ARG;
+  if (d.device < 0) return GZ_ERR_INVALID_ARG;
+  if ((d.flags & GZ_FLAG_EPILOGUE_DIRECT) && (d.flags & GZ_FLAG_EPILOGUE_TMA))
+    return GZ_ERR_INVALID_ARG;
+  if (d.flags & ~(GZ_FLAG_EPILOGUE_DIRECT | GZ_FLAG_EPILOGUE_TMA | 0x80000000u))
+    return GZ_ERR_INVALID_ARG;
+  if (!pair_supported(d.in_type, d.out_type)) return GZ_ERR_UNSUPPORTED;
+  if (d.config != GZ_CFG_AUTO && d.config != GZ_CFG_SIMT && !shape_of(d.config))
+    return GZ_ERR_INVALID_ARG;
+  const int64_t min_lda = d.layout_a == GZ_ROW_MAJOR ? d.k : d.m;
+  const int64_t min_ldb = d.layout_b == GZ_ROW_MAJOR ? d.n : d.k;
+  if (d.lda == 0) d.lda = min_lda;
+  if (d.ldb == 0) d.ldb = min_ldb;
+  if (d.ldc == 0) d.ldc = d.n;
+  if (d.ldd == 0) d.ldd = d.n;
+  if (d.lda < min_lda || d.ldb < min_ldb || d.ldc < d.n || d.ldd < d.n) return GZ_ERR_INVALID_ARG;
+  // Tile coordinates and TMA coordinates are 32-bit.
+  const int64_t lim = (int64_t(1) << 31) - 1024;
+  if (d.m > lim || d.n > lim || d.k > lim) return GZ_ERR_TOO_LARGE;
+  if (cdiv(d.m, 128) * cdiv(d.n, 64) > (int64_t(1) << 31) - 1) return GZ_ERR_TOO_LARGE;
+  if (d.wait_limit_ns == 0) d.wait_limit_ns = 2000000000ull;
+  pr->d = d;
+  pr->in_size = dtype_size(d.in_type);
+  pr->out_size = dtype_size(d.out_type);
+  pr->a_mn_major = d.layout_a == GZ_COL_MAJOR;
+  pr->b_mn_major = d.layout_b == GZ_ROW_MAJOR;
+  pr->tma_ld_ok = (d.lda * pr->in_size) % 16 == 0 && (d.ldb * pr->in_size) % 16 == 0 &&
+                  (d.lda * (int64_t)pr->in_size) < (int64_t(1) << 40) &&
+                  (d.ldb * (int64_t)pr->in_size) < (int64_t(1) << 40);
+  return GZ_OK;
+}
+
+// An M/N-contiguous operand is fetched in 128-byte chunks of its tile edge, so the
+// edge (in elements) must hold at least one chunk: 128 for s8, 64 for 16-bit, 32 for fp32.
+bool shape_fits(const Problem& pr, const CfgShape& s) {
+  const int chunk = 128 / pr.in_size;
+  if (pr.b_mn_major && (s.bn / s.ctas) % chunk != 0) return false;
+  if (pr.a_mn_major && 128 % chunk != 0) return false;
+  return true;
+}
+
+// Pick the tile shape with the least estimated time: waves of tiles over the
+// SMs, each wave costing the per-SM tile area divided by the shape's efficiency.
+int choose_config(const Problem& pr, int sm_count) {
+  if (!pr.tma_ld_ok) return GZ_CFG_SIMT;
+  double best = 0;
+  int best_cfg = GZ_CFG_1CTA_N128;
+  for (const auto& s : kShapes) {
+    if (!shape_fits(pr, s)) continue;
+    const int64_t tiles = cdiv(pr.d.m, 128 * s.ctas) * cdiv(pr.d.n, s.bn);
+    const int64_t units = sm_count / s.ctas;
+    if (units <= 0) continue;
+    const int64_t waves = cdiv(tiles, units);
+    const double cost = double(waves) * (128.0 * s.bn) / s.eff;
+    if (best == 0 || cost < best) {
+      best = cost;
+      best_cfg = s.config;
+    }
+  }
+  return best_cfg;
+}
+
+void fill_info(const Problem& pr, int config, int sm_count, gz_plan_info* info) {
+  std::memset(info, 0, sizeof(*info));
+  info->config = config;
+  info->sm_count = sm_count;
+  info->lda = pr.d.lda;
+  info->ldb = pr.d.ldb;
+  info->ldc = pr.d.ldc;
+  info->ldd = pr.d.ldd;
+  if (config == GZ_CFG_SIMT) {
+    info->tile_m = 64;
+    info->tile_n = 64;
+    info->tile_k = 16;
+    info->stages = 1;
+    info->ctas_per_tile = 1;
+    info->tiles = cdiv(pr.d.m, 64) * cdiv(pr.d.n, 64);
+    info->grid = (int32_t)info->tiles;
+    info->smem_bytes = 0;
+    return;
+  }
+  const CfgShape* s = shape_of(config);
+  info->tile_m = 128 * s->ctas;
+  info->tile_n = s->bn;
+  info->tile_k = 128 / pr.in_size;
+  info->stages = s->stages;
+  info->ctas_per_tile = s->ctas;
+  info->tiles = cdiv(pr.d.m, info->tile_m) * cdiv(pr.d.n, s->bn);
+  const int64_t units = sm_count / s->ctas;
+  info->grid = (int32_t)((info->tiles < units ? info->tiles : units) * s->ctas);
+  info->smem_bytes = 1024 + s->stages * (128 * 128 + (s->bn / s->ctas) * 128) + 4 * 2 * 4096 + 256;
+  const bool d_tma_ok = (pr.d.ldd * pr.out_size) % 16 == 0;
+  info->epilogue_tma = (pr.d.flags & GZ_FLAG_EPILOGUE_DIRECT) ? 0 : (d_tma_ok ? 1 : 0);
+}
+
+using LaunchFn = cudaError_t (*)(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
+                                 const gz::GemmParams&, int grid, cudaStream_t);
+using AttrFn = cudaError_t (*)();
+
+template <class Cfg>
+cudaError_t set_attr() {
+  return cudaFuncSetAttribute(gz::sm100_gemm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              Cfg::SMEM_BYTES);
+}
+
+template <class Cfg>
+cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
+                   const gz::GemmParams& p, int grid, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = Cfg::CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gz::sm100_gemm_kernel<Cfg>, ta, tb, td, p);
+}
+
+struct KernelEntry {
+  LaunchFn launch;
+  AttrFn attr;
+};
+
+template <gz::ptx::Kind KIND, typename TOut>
+KernelEntry entry_for_shape(int config) {
+  switch (config) {
+    case GZ_CFG_2CTA_N256: {
+      using C = gz::GemmCfg<KIND, TOut, 256, 2, 6>;
+      return {launch<C>, set_attr<C>};
+    }
+    case GZ_CFG_1CTA_N256: {
+      using C = gz::GemmCfg<KIND, TOut, 256, 1, 4>;
+      return {launch<C>, set_attr<C>};
+    }
+    case GZ_CFG_2CTA_N128: {
+      using C = gz::GemmCfg<KIND, TOut, 128, 2, 8>;
+      return {launch<C>, set_attr<C>};
+    }
+    case GZ_CFG_1CTA_N128: {
+      using C = gz::GemmCfg<KIND, TOut, 128, 1, 6>;
+      return {launch<C>, set_attr<C>};
+    }
+    case GZ_CFG_1CTA_N64: {
+      using C = gz::GemmCfg<KIND, TOut, 64, 1, 8>;
+      return {launch<C>, set_attr<C>};
+    }
+  }
+  return {nullptr, nullptr};
+}
+
+KernelEntry entry_for(int in, int out, int config) {
+  using gz::ptx::Kind;
+  if (in == GZ_DT_F16 && out == GZ_DT_F16) return entry_for_shape<Kind::F16, __half>(config);
+  if (in == GZ_DT_BF16 && out == GZ_DT_BF16) return entry_for_shape<Kind::F16, __nv_bfloat16>(config);
+  if ((in == GZ_DT_F16 || in == GZ_DT_BF16) && out == GZ_DT_F32)
+    return entry_for_shape<Kind::F16, float>(config);
+  if (in == GZ_DT_F32) return entry_for_shape<Kind::TF32, float>(config);
+  if (in == GZ_DT_S8) return entry_for_shape<Kind::I8, int32_t>(config);
+  return {nullptr, nullptr};
+}
+
+template <typename TIn, typename TOut>
+cudaError_t launch_simt(const gz::SimtParams& sp, cudaStream_t stream) {
+  dim3 grid((unsigned)cdiv(sp.n, 64), (unsigned)cdiv(sp.m, 64), 1);
+  gz::simt_gemm_kernel<TIn, TOut><<<grid, 256, 0, stream>>>(sp);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_simt_any(int in, int out, const gz::SimtParams& sp, cudaStream_t stream) {
+  if (in == GZ_DT_F16 && out == GZ_DT_F16) return launch_simt<__half, __half>(sp, stream);
+  if (in == GZ_DT_F16 && out == GZ_DT_F32) return launch_simt<__half, float>(sp, stream);
+  if (in == GZ_DT_BF16 && out == GZ_DT_BF16)
+    return launch_simt<__nv_bfloat16, __nv_bfloat16>(sp, stream);
+  if (in == GZ_DT_BF16 && out == GZ_DT_F32) return launch_simt<__nv_bfloat16, float>(sp, stream);
+  if (in == GZ_DT_F32) return launch_simt<float, float>(sp, stream);
+  if (in == GZ_DT_S8) return launch_simt<int8_t, int32_t>(sp, stream);
+  return cudaErrorInvalidValue;
+}
+
+CUtensorMapDataType tmap_type(int dt) {
+  switch (dt) {
+    case GZ_DT_F16: return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    case GZ_DT_BF16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    case GZ_DT_F32: return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    case GZ_DT_S32: return CU_TENSOR_MAP_DATA_TYPE_INT32;
+    default: return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  }
+}
+
+// 2-D tensor map: dim0 (contiguous) x dim1, row pitch `pitch_bytes`, 128-byte swizzle.
+bool encode_2d(CUtensorMap* tm, int dt, const void* base, uint64_t dim0, uint64_t dim1,
+               uint64_t pitch_bytes, uint32_t box0, uint32_t box1, bool promote) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    g_last_cuda_error = "cuTensorMapEncodeTiled entry point not available";
+    return false;
+  }
+  cuuint64_t dims[2] = {dim0, dim1};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box0, box1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, tmap_type(dt), 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  promote ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[96];
+    std::snprintf(buf, sizeof(buf), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    g_last_cuda_error = buf;
+    return false;
+  }
+  return true;
+}
+
+}  // namespace
+
+struct gz_plan {
+  Problem pr;
+  gz_plan_info info;
+  KernelEntry entry;
+  gz::GemmParams base;  // everything that does not depend on the operand pointers
+  uint32_t* status_dev;
+  // device staging for gz_gemm_run_host
+  void *ha, *hb, *hc, *hd;
+  size_t ha_bytes, hb_bytes, hcd_bytes;
+  std::mutex mu;
+};
+
+namespace {
+
+void build_operand(gz::OperandDesc* od, bool mn_major, int rows, int in_size) {
+  const int bk = 128 / in_size;  // K elements per 128 bytes
+  od->mn_major = mn_major ? 1u : 0u;
+  const uint32_t sbo = 1024u >> 4;  // 8 rows of 128 bytes between core-matrix groups
+  if (!mn_major) {
+    // K contiguous: one box of `rows` x 128 bytes; a K step moves 32 bytes inside the swizzle atom.
+    od->boxes = 1;
+    od->box_mn = rows;
+    od->box_bytes = rows * 128;
+    od->desc_lo = 1u << 16;  // leading byte offset is unused for swizzled K-major operands
+    od->k_step16 = 32u >> 4;
+  } else {
+    // M/N contiguous: boxes of (128 bytes of M/N) x (bk rows of K), one per 128-byte chunk of the
+    // tile edge; an MMA K step moves whole 8-row groups.
+    const int mn_per_box = 128 / in_size;
+    od->boxes = rows / mn_per_box;
+    od->box_mn = mn_per_box;
+    od->box_bytes = bk * 128;
+    od->desc_lo = ((od->box_bytes >> 4) & 0x3FFFu) << 16;  // distance between M/N chunks
+    const int umma_k = 32 / in_size;
+    od->k_step16 = (uint32_t)(umma_k * 128) >> 4;
+  }
+  od->desc_hi = sbo | (1u << 14) /* descriptor version for sm_100 */ | (2u << 29) /* 128B swizzle */;
+}
+
+uint32_t build_idesc(const Problem& pr, const CfgShape& s) {
+  uint32_t fmt_ab, fmt_c;
+  switch (pr.d.in_type) {
+    case GZ_DT_F16: fmt_ab = 0; fmt_c = 1; break;
+    case GZ_DT_BF16: fmt_ab = 1; fmt_c = 1; break;
+    case GZ_DT_F32: fmt_ab = 2; fmt_c = 1; break;  // tf32 operands, f32 accumulate
+    default: fmt_ab = 1; fmt_c = 2; break;         // signed 8-bit operands, s32 accumulate
+  }
+  uint32_t idesc = 0;
+  idesc |= fmt_c << 4;
+  idesc |= fmt_ab << 7;
+  idesc |= fmt_ab << 10;
+  idesc |= (pr.a_mn_major ? 1u : 0u) << 15;
+  idesc |= (pr.b_mn_major ? 1u : 0u) << 16;
+  idesc |= (uint32_t)(s.bn >> 3) << 17;
+  idesc |= (uint32_t)((128 * s.ctas) >> 4) << 24;
+  return idesc;
+}
+
+gz_status read_scalars(const Problem& pr, const void* alpha, const void* beta, float* af, float* bf,
+                       int32_t* ai, int32_t* bi) {
+  if (!alpha || !beta) return GZ_ERR_INVALID_ARG;
+  *af = *bf = 0.f;
+  *ai = *bi = 0;
+  if (pr.d.in_type == GZ_DT_S8) {
+    *ai = *static_cast<const int32_t*>(alpha);
+    *bi = *static_cast<const int32_t*>(beta);
+  } else {
+    *af = *static_cast<const float*>(alpha);
+    *bf = *static_cast<const float*>(beta);
+  }
+  return GZ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+GZ_API int32_t gz_version(void) { return 100; }
+
+GZ_API const char* gz_status_string(gz_status s) {
+  switch (s) {
+    case GZ_OK: return "ok";
+    case GZ_ERR_INVALID_ARG: return "invalid argument";
+    case GZ_ERR_UNSUPPORTED: return "unsupported data type combination or configuration";
+    case GZ_ERR_MISALIGNED: return "pointer is not aligned to its element size";
+    case GZ_ERR_CUDA: return "CUDA call failed";
+    case GZ_ERR_DEVICE_TIMEOUT: return "a bounded wait inside the kernel expired";
+    case GZ_ERR_NO_DEVICE: return "no CUDA device of compute capability 10.x";
+    case GZ_ERR_TOO_LARGE: return "extent too large";
+    case GZ_ERR_OUT_OF_MEMORY: return "out of memory";
+  }
+  return "unknown status";
+}
+
+GZ_API const char* gz_last_cuda_error(void) { return g_last_cuda_error.c_str(); }
+
+GZ_API void gz_tile_coords(uint32_t tiles_m, uint32_t tiles_n, uint32_t group_m, uint32_t t,
+                           uint32_t* tile_m, uint32_t* tile_n) {
+  gz::TileGrid g{tiles_m, tiles_n, group_m ? group_m : 1u, tiles_m * tiles_n};
+  uint32_t tm = 0, tn = 0;
+  gz::tile_coords(g, t, tm, tn);
+  if (tile_m) *tile_m = tm;
+  if (tile_n) *tile_n = tn;
+}
+
+GZ_API gz_status gz_partition_columns(int64_t n, int32_t parts, int32_t p, int64_t align,
+                                      int64_t* begin, int64_t* end) {
+  if (n <= 0 || parts <= 0 || p < 0 || p >= parts || align <= 0 || !begin || !end)
+    return GZ_ERR_INVALID_ARG;
+  // Distribute whole `align`-column blocks; the first (blocks % parts) parts get one more.
+  const int64_t blocks = cdiv(n, align);
+  const int64_t q = blocks / parts, r = blocks % parts;
+  const int64_t b0 = p * q + (p < r ? p : r);
+  const int64_t b1 = b0 + q + (p < r ? 1 : 0);
+  int64_t lo = b0 * align, hi = b1 * align;
+  if (lo > n) lo = n;
+  if (hi > n) hi = n;
+  *begin = lo;
+  *end = hi;
+  return GZ_OK;
+}
+
+GZ_API gz_status gz_gemm_desc_validate(const gz_gemm_desc* desc, int sm_count, gz_plan_info* info) {
+  Problem pr;
+  gz_status st = normalise(desc, &pr);
+  if (st != GZ_OK) return st;
+  if (sm_count <= 0) sm_count = 148;
+  int config = pr.d.config;
+  if (config == GZ_CFG_AUTO) config = choose_config(pr, sm_count);
+  if (config != GZ_CFG_SIMT && !pr.tma_ld_ok) return GZ_ERR_MISALIGNED;
+  if (config != GZ_CFG_SIMT && !shape_fits(pr, *shape_of(config))) return GZ_ERR_UNSUPPORTED;
+  if (info) fill_info(pr, config, sm_count, info);
+  return GZ_OK;
+}
+
+GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
+  if (!out) return GZ_ERR_INVALID_ARG;
+  *out = nullptr;
+  Problem pr;
+  gz_status st = normalise(desc, &pr);
+  if (st != GZ_OK) return st;
+
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+    (void)cudaGetLastError();
+    return GZ_ERR_NO_DEVICE;
+  }
+  if (pr.d.device >= ndev) return GZ_ERR_INVALID_ARG;
+  cudaDeviceProp prop;
+  if (!cuda_ok(cudaGetDeviceProperties(&prop, pr.d.device), "cudaGetDeviceProperties"))
+    return GZ_ERR_CUDA;
+  if (prop.major != 10) return GZ_ERR_NO_DEVICE;
+  if (!cuda_ok(cudaSetDevice(pr.d.device), "cudaSetDevice")) return GZ_ERR_CUDA;
+
+  const int sm_count = prop.multiProcessorCount;
+  int config = pr.d.config;
+  if (config == GZ_CFG_AUTO) config = choose_config(pr, sm_count);
+  if (config != GZ_CFG_SIMT && !pr.tma_ld_ok) return GZ_ERR_MISALIGNED;
+  if (config != GZ_CFG_SIMT && !shape_fits(pr, *shape_of(config))) return GZ_ERR_UNSUPPORTED;
+
+  gz_plan* pl = new (std::nothrow) gz_plan();
+  if (!pl) return GZ_ERR_OUT_OF_MEMORY;
+  pl->pr = pr;
+  pl->status_dev = nullptr;
+  pl->ha = pl->hb = pl->hc = pl->hd = nullptr;
+  pl->ha_bytes = pl->hb_bytes = pl->hcd_bytes = 0;
+  fill_info(pr, config, sm_count, &pl->info);
+  std::memset(&pl->base, 0, sizeof(pl->base));
+  pl->entry = {nullptr, nullptr};
+
+  if (!cuda_ok(cudaMalloc(&pl->status_dev, 4 * sizeof(uint32_t)), "cudaMalloc(status)") ||
+      !cuda_ok(cudaMemset(pl->status_dev, 0, 4 * sizeof(uint32_t)), "cudaMemset(status)")) {
+    if (pl->status_dev) cudaFree(pl->status_dev);
+    delete pl;
+    return GZ_ERR_CUDA;
+  }
+
+  if (config != GZ_CFG_SIMT) {
+    const CfgShape& s = *shape_of(config);
+    pl->entry = entry_for(pr.d.in_type, pr.d.out_type, config);
+    if (!pl->entry.launch) {
+      cudaFree(pl->status_dev);
+      delete pl;
+      return GZ_ERR_UNSUPPORTED;
+    }
+    if (!cuda_ok(pl->entry.attr(), "cudaFuncSetAttribute(max dynamic shared memory)")) {
+      cudaFree(pl->status_dev);
+      delete pl;
+      return GZ_ERR_CUDA;
+    }
+    gz::GemmParams& p = pl->base;
+    build_operand(&p.a, pr.a_mn_major, 128, pr.in_size);
+    build_operand(&p.b, pr.b_mn_major, s.bn / s.ctas, pr.in_size);
+    const uint32_t tile_m = 128u * s.ctas;
+    p.grid.tiles_m = (uint32_t)cdiv(pr.d.m, tile_m);
+    p.grid.tiles_n = (uint32_t)cdiv(pr.d.n, s.bn);
+    // Rows of tiles that run concurrently should span about as many output rows as columns.
+    uint32_t gm = 2048u / tile_m;
+    p.grid.group_m = gm < 1 ? 1 : gm;
+    p.grid.num_tiles = p.grid.tiles_m * p.grid.tiles_n;
+    p.m = (uint32_t)pr.d.m;
+    p.n = (uint32_t)pr.d.n;
+    p.k = (uint32_t)pr.d.k;
+    p.bk = 128u / pr.in_size;
+    p.k_blocks = (uint32_t)cdiv(pr.d.k, p.bk);
+    p.idesc = build_idesc(pr, s);
+    p.epilogue_tma = pl->info.epilogue_tma;
+    p.test_flags = (pr.d.flags & 0x80000000u) ? 1u : 0u;
+    p.ldc = pr.d.ldc;
+    p.ldd = pr.d.ldd;
+    p.status = pl->status_dev;
+    p.wait_limit_ns = pr.d.wait_limit_ns;
+  }
+  *out = pl;
+  return GZ_OK;
+}
+
+GZ_API gz_status gz_gemm_plan_destroy(gz_plan* pl) {
+  if (!pl) return GZ_ERR_INVALID_ARG;
+  (void)cudaSetDevice(pl->pr.d.device);
+  if (pl->status_dev) cudaFree(pl->status_dev);
+  if (pl->ha) cudaFree(pl->ha);
+  if (pl->hb) cudaFree(pl->hb);
+  if (pl->hc) cudaFree(pl->hc);
+  if (pl->hd) cudaFree(pl->hd);
+  delete pl;
+  return GZ_OK;
+}
+
+GZ_API gz_status gz_gemm_plan_info(const gz_plan* pl, gz_plan_info* info) {
+  if (!pl || !info) return GZ_ERR_INVALID_ARG;
+  *info = pl->info;
+  return GZ_OK;
+}
+
+GZ_API gz_status gz_gemm_run(gz_plan* pl, const void* a, const void* b, const void* c, void* d,
+                             const void* alpha, const void* beta, void* stream_v) {
+  if (!pl || !a || !b || !d) return GZ_ERR_INVALID_ARG;
+  const Problem& pr = pl->pr;
+  float af, bf;
+  int32_t ai, bi;
+  gz_status st = read_scalars(pr, alpha, beta, &af, &bf, &ai, &bi);
+  if (st != GZ_OK) return st;
+  const bool beta_zero = (pr.d.in_type == GZ_DT_S8) ? (bi == 0) : (bf == 0.0f);
+  if (!beta_zero && !c) return GZ_ERR_INVALID_ARG;
+  auto misaligned = [](const void* p, int sz) { return (reinterpret_cast<uintptr_t>(p) % sz) != 0; };
+  if (misaligned(a, pr.in_size) || misaligned(b, pr.in_size) || misaligned(d, pr.out_size) ||
+      (c && misaligned(c, pr.out_size)))
+    return GZ_ERR_MISALIGNED;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess || cur != pr.d.device) {
+    if (!cuda_ok(cudaSetDevice(pr.d.device), "cudaSetDevice")) return GZ_ERR_CUDA;
+  }
+
+  const bool tma_ptr_ok = (reinterpret_cast<uintptr_t>(a) % 16 == 0) &&
+                          (reinterpret_cast<uintptr_t>(b) % 16 == 0);
+  if (pl->info.config == GZ_CFG_SIMT || !tma_ptr_ok) {
+    gz::SimtParams sp;
+    sp.a = a;
+    sp.b = b;
+    sp.c = beta_zero ? nullptr : c;
+    sp.d = d;
+    sp.m = pr.d.m;
+    sp.n = pr.d.n;
+    sp.k = pr.d.k;
+    sp.a_sm = pr.a_mn_major ? 1 : pr.d.lda;
+    sp.a_sk = pr.a_mn_major ? pr.d.lda : 1;
+    sp.b_sk = pr.b_mn_major ? pr.d.ldb : 1;
+    sp.b_sn = pr.b_mn_major ? 1 : pr.d.ldb;
+    sp.ldc = pr.d.ldc;
+    sp.ldd = pr.d.ldd;
+    sp.alpha_f = af;
+    sp.beta_f = bf;
+    sp.alpha_i = ai;
+    sp.beta_i = bi;
+    if (!cuda_ok(launch_simt_any(pr.d.in_type, pr.d.out_type, sp, stream), "simt launch"))
+      return GZ_ERR_CUDA;
+    return GZ_OK;
+  }
+
+  const CfgShape& s = *shape_of(pl->info.config);
+  gz::GemmParams p = pl->base;
+  p.alpha_f = af;
+  p.beta_f = bf;
+  p.alpha_i = ai;
+  p.beta_i = bi;
+  p.c = beta_zero ? nullptr : c;
+  p.d = d;
+  p.c_vec_ok = (c && reinterpret_cast<uintptr_t>(c) % 16 == 0 && (pr.d.ldc * pr.out_size) % 16 == 0) ? 1u : 0u;
+  p.d_vec_ok = (reinterpret_cast<uintptr_t>(d) % 16 == 0 && (pr.d.ldd * pr.out_size) % 16 == 0) ? 1u : 0u;
+  if (p.epilogue_tma && reinterpret_cast<uintptr_t>(d) % 16 != 0) p.epilogue_tma = 0;
+
+  CUtensorMap ta, tb, td;
+  const uint32_t bk = 128u / pr.in_size;
+  bool ok;
+  if (!pr.a_mn_major)
+    ok = encode_2d(&ta, pr.d.in_type, a, (uint64_t)pr.d.k, (uint64_t)pr.d.m,
+                   (uint64_t)pr.d.lda * pr.in_size, bk, 128, true);
+  else
+    ok = encode_2d(&ta, pr.d.in_type, a, (uint64_t)pr.d.m, (uint64_t)pr.d.k,
+                   (uint64_t)pr.d.lda * pr.in_size, p.a.box_mn, bk, true);
+  if (!ok) return GZ_ERR_CUDA;
+  if (!pr.b_mn_major)
+    ok = encode_2d(&tb, pr.d.in_type, b, (uint64_t)pr.d.k, (uint64_t)pr.d.n,
+                   (uint64_t)pr.d.ldb * pr.in_size, bk, (uint32_t)(s.bn / s.ctas), true);
+  else
+    ok = encode_2d(&tb, pr.d.in_type, b, (uint64_t)pr.d.n, (uint64_t)pr.d.k,
+                   (uint64_t)pr.d.ldb * pr.in_size, p.b.box_mn, bk, true);
+  if (!ok) return GZ_ERR_CUDA;
+  if (p.epilogue_tma) {
+    ok = encode_2d(&td, pr.d.out_type, d, (uint64_t)pr.d.n, (uint64_t)pr.d.m,
+                   (uint64_t)pr.d.ldd * pr.out_size, 128u / pr.out_size, 32, false);
+    if (!ok) return GZ_ERR_CUDA;
+  } else {
+    td = ta;  // unused by the kernel in this mode
+  }
+  if (!cuda_ok(pl->entry.launch(ta, tb, td, p, pl->info.grid, stream), "kernel launch"))
+    return GZ_ERR_CUDA;
+  return GZ_OK;
+}
+
+GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, const void* c, void* d,
+                                  const void* alpha, const void* beta, void* stream_v) {
+  if (!pl || !a || !b || !d) return GZ_ERR_INVALID_ARG;
+  const Problem& pr = pl->pr;
+  float af, bf;
+  int32_t ai, bi;
+  gz_status st = read_scalars(pr, alpha, beta, &af, &bf, &ai, &bi);
+  if (st != GZ_OK) return st;
+  const bool beta_zero = (pr.d.in_type == GZ_DT_S8) ? (bi == 0) : (bf == 0.0f);
+  if (!beta_zero && !c) return GZ_ERR_INVALID_ARG;
+  if (!cuda_ok(cudaSetDevice(pr.d.device), "cudaSetDevice")) return GZ_ERR_CUDA;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  const size_t a_rows = pr.a_mn_major ? pr.d.k : pr.d.m;
+  const size_t b_rows = pr.b_mn_major ? pr.d.k : pr.d.n;
+  const size_t a_bytes = a_rows * pr.d.lda * pr.in_size;
+  const size_t b_bytes = b_rows * pr.d.ldb * pr.in_size;
+  const size_t c_bytes = (size_t)pr.d.m * pr.d.ldc * pr.out_size;
+  const size_t d_bytes = (size_t)pr.d.m * pr.d.ldd * pr.out_size;
+  {
+    std::lock_guard<std::mutex> lock(pl->mu);
+    if (!pl->ha) {
+      const size_t cd = c_bytes > d_bytes ? c_bytes : d_bytes;
+      if (!cuda_ok(cudaMalloc(&pl->ha, a_bytes), "cudaMalloc(A staging)") ||
+          !cuda_ok(cudaMalloc(&pl->hb, b_bytes), "cudaMalloc(B staging)") ||
+          !cuda_ok(cudaMalloc(&pl->hc, cd), "cudaMalloc(C staging)") ||
+          !cuda_ok(cudaMalloc(&pl->hd, cd), "cudaMalloc(D staging)"))
+        return GZ_ERR_OUT_OF_MEMORY;
+    }
+  }
+  if (!cuda_ok(cudaMemcpyAsync(pl->ha, a, a_bytes, cudaMemcpyHostToDevice, stream), "H2D A") ||
+      !cuda_ok(cudaMemcpyAsync(pl->hb, b, b_bytes, cudaMemcpyHostToDevice, stream), "H2D B"))
+    return GZ_ERR_CUDA;
+  if (!beta_zero &&
+      !cuda_ok(cudaMemcpyAsync(pl->hc, c, c_bytes, cudaMemcpyHostToDevice, stream), "H2D C"))
+    return GZ_ERR_CUDA;
+  st = gz_gemm_run(pl, pl->ha, pl->hb, beta_zero ? nullptr : pl->hc, pl->hd, alpha, beta, stream_v);
+  if (st != GZ_OK) return st;
+  if (!cuda_ok(cudaMemcpyAsync(d, pl->hd, d_bytes, cudaMemcpyDeviceToHost, stream), "D2H D") ||
+      !cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize"))
+    return GZ_ERR_CUDA;
+  return GZ_OK;
+}
+
+GZ_API gz_status gz_last_device_status(gz_plan* pl, void* stream_v, uint32_t detail[4]) {
+  if (!pl) return GZ_ERR_INVALID_ARG;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (!cuda_ok(cudaSetDevice(pl->pr.d.device), "cudaSetDevice")) return GZ_ERR_CUDA;
+  uint32_t h[4] = {0, 0, 0, 0};
+  if (!cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize") ||
+      !cuda_ok(cudaMemcpy(h, pl->status_dev, sizeof(h), cudaMemcpyDeviceToHost), "read status"))
+    return GZ_ERR_CUDA;
+  if (detail) std::memcpy(detail, h, sizeof(h));
+  if (h[0] != 0) {
+    (void)cudaMemset(pl->status_dev, 0, sizeof(h));
+    return GZ_ERR_DEVICE_TIMEOUT;
+  }
+  return GZ_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ fills
+namespace {
+
+template <typename T>
+__device__ __forceinline__ T fill_cast(float v);
+template <>
+__device__ __forceinline__ float fill_cast<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half fill_cast<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 fill_cast<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ int8_t fill_cast<int8_t>(float v) {
+  return static_cast<int8_t>(fmaxf(-128.f, fminf(127.f, rintf(v))));
+}
+template <>
+__device__ __forceinline__ int32_t fill_cast<int32_t>(float v) {
+  return static_cast<int32_t>(rintf(v));
+}
+
+template <typename T>
+__global__ void fill_kernel(T* ptr, int64_t count, uint64_t seed, uint32_t stream_id, int dist,
+                            float scale) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+       i += stride) {
+    const uint64_t bits = gz::rng_bits(seed, stream_id, static_cast<uint64_t>(i));
+    float v;
+    if (dist == 0) {
+      v = gz::rng_uniform_pm1(bits) * scale;
+    } else if (dist == 1) {
+      // Box-Muller on two 24-bit uniforms taken from the same 64 random bits.
+      const float u1 = (static_cast<float>(static_cast<uint32_t>(bits >> 40)) + 1.0f) * (1.0f / 16777216.0f);
+      const float u2 = static_cast<float>(static_cast<uint32_t>(bits >> 16) & 0xFFFFFFu) * (1.0f / 16777216.0f);
+      v = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2) * scale;
+    } else {
+      if (sizeof(T) == 1) v = static_cast<float>(gz::rng_int8(bits));
+      else {
+        const int32_t span = 2 * static_cast<int32_t>(scale) + 1;
+        v = static_cast<float>(static_cast<int32_t>((bits >> 33) % static_cast<uint64_t>(span)) -
+                               static_cast<int32_t>(scale));
+      }
+    }
+    ptr[i] = fill_cast<T>(v);
+  }
+}
+
+}  // namespace
+
+extern "C" GZ_API gz_status gz_fill(void* ptr, int32_t dtype, int64_t count, uint64_t seed,
+                                    uint32_t stream_id, int32_t dist, float scale, void* stream_v) {
+  if (!ptr || count < 0 || dist < 0 || dist > 2 || dtype_size(dtype) == 0) return GZ_ERR_INVALID_ARG;
+  if (count == 0) return GZ_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int block = 256;
+  int64_t want = cdiv(count, block);
+  const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
+  switch (dtype) {
+    case GZ_DT_F16:
+      fill_kernel<__half><<<grid, block, 0, stream>>>((__half*)ptr, count, seed, stream_id, dist, scale);
+      break;
+    case GZ_DT_BF16:
+      fill_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>((__nv_bfloat16*)ptr, count, seed, stream_id, dist, scale);
+      break;
+    case GZ_DT_F32:
+      fill_kernel<float><<<grid, block, 0, stream>>>((float*)ptr, count, seed, stream_id, dist, scale);
+      break;
+    case GZ_DT_S8:
+      fill_kernel<int8_t><<<grid, block, 0, stream>>>((int8_t*)ptr, count, seed, stream_id, dist, scale);
+      break;
+    case GZ_DT_S32:
+      fill_kernel<int32_t><<<grid, block, 0, stream>>>((int32_t*)ptr, count, seed, stream_id, dist, scale);
+      break;
+  }
+  if (!cuda_ok(cudaGetLastError(), "fill launch")) return GZ_ERR_CUDA;
+  return GZ_OK;
+}

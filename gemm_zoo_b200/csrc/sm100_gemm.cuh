@@ -1,0 +1,586 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a:
+//   D = alpha * A * B + beta * C
+//
+// This kernel takes the place of the three mma.sync kernels of the reference
+// (nvidia/kernels/sm_80/bf16_mma_gemm.cuh:16-265, fp16_mma_gemm.cuh:14-305,
+// tf32_mma_gemm.cuh:15-260) and of the s8 contract of
+// intel/kernels/xe_gemm_s8_s8_s32_m8k16.hpp:17-77.  Same outer shape as those
+// (persistent CTAs, multi-stage operand ring, fused alpha/beta epilogue,
+// next tile's loads overlapping this tile's epilogue), different machinery:
+//
+//   warp 0      one lane issues TMA tile loads (128-byte-swizzled boxes) into a
+//               STAGES-deep shared-memory ring; completion is counted in bytes
+//               on the stage's "full" mbarrier.
+//   warp 1      allocates TMEM; one lane (of the leader CTA when two CTAs share
+//               a tile) issues tcgen05.mma from shared-memory descriptors into
+//               one of two TMEM accumulators and commits each stage back to its
+//               "empty" mbarrier.
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (each warp owns
+//               the 32 TMEM lanes of its warp_id % 4 quadrant), apply
+//               alpha/beta in fp32 (int32 for s8), cast, and either stage rows
+//               in swizzled shared memory for a TMA store or store directly.
+//
+// The second accumulator lets the epilogue of tile i run under the main loop
+// of tile i+1.  No cluster-multicast load is used anywhere: with CTAS == 2 each
+// CTA of the pair loads its own 128 rows of A and its own half of the B tile.
+//
+// Every wait on an mbarrier is bounded (Params::wait_limit_ns).  When a wait
+// expires the waiter records a code in Params::status, raises a CTA-wide abort
+// flag that all roles poll, and every role falls through to the common
+// teardown, which still frees TMEM.
+#ifndef GZ_SM100_GEMM_CUH
+#define GZ_SM100_GEMM_CUH
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+#include "tile_sched.h"
+
+namespace gz {
+
+// How one operand tile is fetched by TMA and described to tcgen05.mma.
+struct OperandDesc {
+  uint32_t boxes;      // TMA boxes per stage per CTA
+  uint32_t box_bytes;  // bytes one box deposits in shared memory
+  uint32_t box_mn;     // extent of one box along the M (or N) dimension, in elements
+  uint32_t mn_major;   // 0: K contiguous in memory (coords {k, mn}); 1: M/N contiguous ({mn, k})
+  uint32_t desc_lo;    // shared-memory descriptor bits 16..31 (leading byte offset >> 4) << 16
+  uint32_t desc_hi;    // bits 32..63: stride byte offset >> 4, version 1, 128B swizzle
+  uint32_t k_step16;   // descriptor start-address advance (bytes >> 4) per MMA K step
+};
+
+// Codes written to status[0] when a bounded wait expires.
+enum WaitCode : uint32_t {
+  WAIT_OK = 0,
+  WAIT_PRODUCER_EMPTY = 1,
+  WAIT_MMA_FULL = 2,
+  WAIT_MMA_TMEM_EMPTY = 3,
+  WAIT_EPILOGUE_TMEM_FULL = 4,
+  WAIT_MMA_DRAIN = 5
+};
+
+struct GemmParams {
+  OperandDesc a, b;
+  TileGrid grid;
+  uint32_t m, n, k;
+  uint32_t k_blocks;  // ceil(k / elements per 128 bytes)
+  uint32_t bk;        // K elements per stage
+  uint32_t idesc;     // tcgen05 instruction descriptor
+  uint32_t epilogue_tma;
+  uint32_t c_vec_ok, d_vec_ok;  // 16-byte vector access to C / D rows is legal
+  uint32_t test_flags;          // bit 0: MMA warp withholds the accumulator-ready signal
+  float alpha_f, beta_f;
+  int32_t alpha_i, beta_i;
+  int64_t ldc, ldd;
+  const void* c;
+  void* d;
+  uint32_t* status;  // 4 words in global memory
+  uint64_t wait_limit_ns;
+};
+
+template <ptx::Kind KIND_, typename TOut_, int BN_, int CTAS_, int STAGES_>
+struct GemmCfg {
+  static constexpr ptx::Kind KIND = KIND_;
+  using TOut = TOut_;
+  static constexpr int BN = BN_;        // tile columns (= MMA N)
+  static constexpr int CTAS = CTAS_;    // CTAs sharing one tile (1 or 2)
+  static constexpr int STAGES = STAGES_;
+  static constexpr int BM = 128;                 // tile rows per CTA
+  static constexpr int BN_CTA = BN / CTAS;       // B rows (tile columns) each CTA loads
+  static constexpr int A_BYTES = BM * 128;       // one stage of A: 128 rows x 128 bytes
+  static constexpr int B_BYTES = BN_CTA * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGING_WARP_BYTES = 2 * 4096;  // two 32-row x 128-byte boxes per warp
+  static constexpr int STAGING_BYTES = 4 * STAGING_WARP_BYTES;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TMEM_COLS = 2 * BN;  // two accumulators
+  static constexpr int THREADS = 192;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile N");
+  static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
+                "TMEM allocation must be a power of two");
+  static_assert(8 * (2 * STAGES + 5) + 8 <= BAR_BYTES, "barrier area");
+  static_assert(STAGE_BYTES % 1024 == 0, "stage must keep 1024-byte alignment");
+};
+
+namespace detail {
+
+struct Abort {
+  uint32_t* flag;  // CTA-shared
+  uint32_t* status;
+  uint64_t limit_ns;
+};
+
+__device__ __forceinline__ bool aborted(const Abort& ab) {
+  return *reinterpret_cast<volatile uint32_t*>(ab.flag) != 0;
+}
+
+__device__ __noinline__ void record_timeout(const Abort& ab, uint32_t code, uint32_t tile,
+                                            uint32_t kb) {
+  if (atomicCAS(ab.status, 0u, code) == 0u) {
+    ab.status[1] = blockIdx.x;
+    ab.status[2] = tile;
+    ab.status[3] = kb;
+    __threadfence();
+  }
+  *reinterpret_cast<volatile uint32_t*>(ab.flag) = 1u;
+}
+
+// Wait for `bar` to complete the phase of parity `parity`, for at most
+// ab.limit_ns.  Returns false if the CTA is aborting.
+template <bool CLUSTER_ACQUIRE = false>
+__device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, const Abort& ab, uint32_t code,
+                                     uint32_t tile, uint32_t kb) {
+  auto poll = [&]() {
+    if constexpr (CLUSTER_ACQUIRE) return ptx::mbar_try_wait_cluster(bar, parity);
+    else return ptx::mbar_try_wait(bar, parity);
+  };
+  if (poll()) return true;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (poll()) return true;
+    if ((++spins & 31u) == 0u) {
+      if (aborted(ab)) return false;
+      if (ptx::globaltimer_ns() - t0 > ab.limit_ns) {
+        record_timeout(ab, code, tile, kb);
+        return false;
+      }
+    }
+  }
+}
+
+template <typename TOut>
+struct OutTraits;
+template <>
+struct OutTraits<float> {
+  static constexpr bool INT = false;
+  __device__ static float to_f(float v) { return v; }
+};
+template <>
+struct OutTraits<__half> {
+  static constexpr bool INT = false;
+  __device__ static float to_f(__half v) { return __half2float(v); }
+};
+template <>
+struct OutTraits<__nv_bfloat16> {
+  static constexpr bool INT = false;
+  __device__ static float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+};
+template <>
+struct OutTraits<int32_t> {
+  static constexpr bool INT = true;
+};
+
+// Pack two fp32 values into one 32-bit word of two 16-bit outputs (low = first).
+template <typename TOut>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// alpha * acc + beta * c for one 32-column slice of one row.
+//   v[32]     in:  raw accumulator words;  out: packed output words (32 * sizeof(TOut) / 4 used)
+//   crow      pointer to C(row, col0) (only dereferenced when beta != 0 and row_ok)
+//   ncols     valid columns in this slice (1..32)
+template <typename TOut>
+__device__ __forceinline__ void epilogue_math(uint32_t (&v)[32], const GemmParams& p,
+                                              const TOut* crow, bool row_ok, uint32_t ncols) {
+  using Tr = OutTraits<TOut>;
+  if constexpr (Tr::INT) {
+    const uint32_t alpha = static_cast<uint32_t>(p.alpha_i);
+    const uint32_t beta = static_cast<uint32_t>(p.beta_i);
+    if (beta != 0u && row_ok) {
+      if (ncols == 32 && p.c_vec_ok) {
+        const uint4* c4 = reinterpret_cast<const uint4*>(crow);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const uint4 cv = c4[q];
+          v[4 * q + 0] = alpha * v[4 * q + 0] + beta * cv.x;
+          v[4 * q + 1] = alpha * v[4 * q + 1] + beta * cv.y;
+          v[4 * q + 2] = alpha * v[4 * q + 2] + beta * cv.z;
+          v[4 * q + 3] = alpha * v[4 * q + 3] + beta * cv.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const uint32_t cv = (static_cast<uint32_t>(i) < ncols) ? static_cast<uint32_t>(crow[i]) : 0u;
+          v[i] = alpha * v[i] + beta * cv;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = alpha * v[i];
+    }
+  } else {
+    const float alpha = p.alpha_f;
+    const float beta = p.beta_f;
+    float f[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = alpha * __uint_as_float(v[i]);
+    if (beta != 0.0f && row_ok) {
+      if (ncols == 32 && p.c_vec_ok) {
+        constexpr int PER16 = 16 / sizeof(TOut);  // elements per 16-byte load
+        const uint4* c4 = reinterpret_cast<const uint4*>(crow);
+#pragma unroll
+        for (int q = 0; q < 32 / PER16; ++q) {
+          const uint4 cv = c4[q];
+          const TOut* ce = reinterpret_cast<const TOut*>(&cv);
+#pragma unroll
+          for (int e = 0; e < PER16; ++e)
+            f[q * PER16 + e] = fmaf(beta, Tr::to_f(ce[e]), f[q * PER16 + e]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (static_cast<uint32_t>(i) < ncols) f[i] = fmaf(beta, Tr::to_f(crow[i]), f[i]);
+      }
+    }
+    if constexpr (sizeof(TOut) == 4) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(f[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = pack2<TOut>(f[2 * i], f[2 * i + 1]);
+    }
+  }
+}
+
+// Store one packed 32-column slice of one row straight to global memory.
+template <typename TOut>
+__device__ __forceinline__ void store_direct(const uint32_t (&v)[32], TOut* drow, uint32_t ncols,
+                                             bool vec_ok) {
+  constexpr int WORDS = 32 * sizeof(TOut) / 4;
+  if (ncols == 32 && vec_ok) {
+    uint4* d4 = reinterpret_cast<uint4*>(drow);
+#pragma unroll
+    for (int q = 0; q < WORDS / 4; ++q)
+      d4[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  } else {
+    if constexpr (sizeof(TOut) == 4) {
+      uint32_t* d32 = reinterpret_cast<uint32_t*>(drow);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (static_cast<uint32_t>(i) < ncols) d32[i] = v[i];
+    } else {
+      uint16_t* d16 = reinterpret_cast<uint16_t*>(drow);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (static_cast<uint32_t>(i) < ncols)
+          d16[i] = static_cast<uint16_t>(v[i >> 1] >> (16 * (i & 1)));
+    }
+  }
+}
+
+}  // namespace detail
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                  const __grid_constant__ CUtensorMap tm_d, const GemmParams p) {
+  using TOut = typename Cfg::TOut;
+  constexpr int CTAS = Cfg::CTAS;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int BN = Cfg::BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;  // 128B-swizzle atoms need 1024-byte alignment
+  uint8_t* const smem = smem_raw + (base - raw_addr);
+
+  const uint32_t staging_base = base + STAGES * Cfg::STAGE_BYTES;
+  const uint32_t bars = staging_base + Cfg::STAGING_BYTES;
+  uint8_t* const bars_ptr = smem + STAGES * Cfg::STAGE_BYTES + Cfg::STAGING_BYTES;
+  auto full_bar = [&](uint32_t s) { return bars + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bars + 8u * (STAGES + s); };
+  auto tmem_full_bar = [&](uint32_t b) { return bars + 8u * (2 * STAGES + b); };
+  auto tmem_empty_bar = [&](uint32_t b) { return bars + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t drain_bar = bars + 8u * (2 * STAGES + 4);
+  uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars_ptr + 8 * (2 * STAGES + 5));
+  uint32_t* const abort_flag = tmem_slot + 1;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t rank = (CTAS == 2) ? ptx::cluster_ctarank() : 0u;
+  const uint32_t cluster = (CTAS == 2) ? ptx::cluster_id_x() : blockIdx.x;
+  const uint32_t num_clusters = (CTAS == 2) ? ptx::num_clusters_x() : gridDim.x;
+
+  const detail::Abort ab{abort_flag, p.status, p.wait_limit_ns};
+
+  // ------------------------------------------------------------ set-up
+  if (threadIdx.x == 0) {
+    *abort_flag = 0u;
+    for (uint32_t s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (uint32_t b = 0; b < 2; ++b) {
+      ptx::mbar_init(tmem_full_bar(b), 1);
+      ptx::mbar_init(tmem_empty_bar(b), 128 * CTAS);
+    }
+    ptx::mbar_init(drain_bar, 1);
+    ptx::fence_mbar_init_cluster();
+    ptx::prefetch_tensormap(&tm_a);
+    ptx::prefetch_tensormap(&tm_b);
+    if (p.epilogue_tma) ptx::prefetch_tensormap(&tm_d);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<CTAS>(ptx::smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    ptx::tmem_relinquish<CTAS>();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CTAS == 2) {
+    ptx::cluster_arrive_release();
+    ptx::cluster_wait_acquire();
+  }
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  const uint32_t k_blocks = p.k_blocks;
+  const uint32_t num_tiles = p.grid.num_tiles;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t t = cluster; ok && t < num_tiles; t += num_clusters) {
+        uint32_t tm, tn;
+        tile_coords(p.grid, t, tm, tn);
+        const int32_t row_a = static_cast<int32_t>(tm * (128u * CTAS) + rank * 128u);
+        const int32_t row_b = static_cast<int32_t>(tn * BN + rank * Cfg::BN_CTA);
+        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+          if (!detail::wait(empty_bar(stage), phase ^ 1u, ab, WAIT_PRODUCER_EMPTY, t, kb)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sb = sa + Cfg::A_BYTES;
+          const int32_t k0 = static_cast<int32_t>(kb * p.bk);
+          if constexpr (CTAS == 1) {
+            const uint32_t fb = full_bar(stage);
+            ptx::mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
+            for (uint32_t i = 0; i < p.a.boxes; ++i) {
+              const int32_t mn = row_a + static_cast<int32_t>(i * p.a.box_mn);
+              ptx::tma_load_2d(sa + i * p.a.box_bytes, &tm_a, p.a.mn_major ? mn : k0,
+                               p.a.mn_major ? k0 : mn, fb);
+            }
+            for (uint32_t i = 0; i < p.b.boxes; ++i) {
+              const int32_t mn = row_b + static_cast<int32_t>(i * p.b.box_mn);
+              ptx::tma_load_2d(sb + i * p.b.box_bytes, &tm_b, p.b.mn_major ? mn : k0,
+                               p.b.mn_major ? k0 : mn, fb);
+            }
+          } else {
+            // Both CTAs' bytes are counted on the leader's barrier.
+            const uint32_t fb = ptx::mapa(full_bar(stage), 0);
+            if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
+            for (uint32_t i = 0; i < p.a.boxes; ++i) {
+              const int32_t mn = row_a + static_cast<int32_t>(i * p.a.box_mn);
+              ptx::tma_load_2d_pair(sa + i * p.a.box_bytes, &tm_a, p.a.mn_major ? mn : k0,
+                                    p.a.mn_major ? k0 : mn, fb);
+            }
+            for (uint32_t i = 0; i < p.b.boxes; ++i) {
+              const int32_t mn = row_b + static_cast<int32_t>(i * p.b.box_mn);
+              ptx::tma_load_2d_pair(sb + i * p.b.box_bytes, &tm_b, p.b.mn_major ? mn : k0,
+                                    p.b.mn_major ? k0 : mn, fb);
+            }
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok && rank == 0) {
+        // Aborting: give loads already issued a bounded chance to land before
+        // the CTA's shared memory is released.  (stage, phase) is the next slot
+        // to fill; the STAGES slots before it are the ones that may be in flight.
+        const uint64_t t0 = ptx::globaltimer_ns();
+        for (uint32_t i = 0; i < STAGES; ++i) {
+          const uint32_t s = (stage + STAGES - 1u - i) % STAGES;
+          const uint32_t ph = (s < stage) ? phase : (phase ^ 1u);
+          while (!ptx::mbar_try_wait(full_bar(s), ph)) {
+            if (ptx::globaltimer_ns() - t0 > 2000000ull) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0 && rank == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      bool issued = false;
+      const uint64_t a_hi = static_cast<uint64_t>(p.a.desc_hi) << 32;
+      const uint64_t b_hi = static_cast<uint64_t>(p.b.desc_hi) << 32;
+      for (uint32_t t = cluster; ok && t < num_tiles; t += num_clusters) {
+        if (!detail::wait<CTAS == 2>(tmem_empty_bar(acc), acc_phase ^ 1u, ab, WAIT_MMA_TMEM_EMPTY, t,
+                                     0)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+          if (!detail::wait(full_bar(stage), phase, ab, WAIT_MMA_FULL, t, kb)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sb = sa + Cfg::A_BYTES;
+          const uint32_t a_lo = ((sa >> 4) & 0x3FFFu) | p.a.desc_lo;
+          const uint32_t b_lo = ((sb >> 4) & 0x3FFFu) | p.b.desc_lo;
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {  // 128 bytes of K per stage, 32 bytes per MMA
+            const uint64_t ad = a_hi | static_cast<uint64_t>(a_lo + j * p.a.k_step16);
+            const uint64_t bd = b_hi | static_cast<uint64_t>(b_lo + j * p.b.k_step16);
+            ptx::umma<Cfg::KIND, CTAS>(d_tmem, ad, bd, p.idesc, (kb | j) != 0u ? 1u : 0u);
+          }
+          issued = true;
+          // Release the stage to the producer(s) once these MMAs have read it.
+          ptx::tc_commit<CTAS>(empty_bar(stage));
+          if constexpr (CTAS == 2) ptx::tc_commit<CTAS>(ptx::mapa(empty_bar(stage), 1));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        if (!(p.test_flags & 1u)) {
+          ptx::tc_commit<CTAS>(tmem_full_bar(acc));
+          if constexpr (CTAS == 2) ptx::tc_commit<CTAS>(ptx::mapa(tmem_full_bar(acc), 1));
+        }
+        acc ^= 1u;
+        if (acc == 0u) acc_phase ^= 1u;
+      }
+      if ((!ok || (p.test_flags & 1u)) && issued) {
+        // Aborting with MMAs possibly in flight: wait (bounded) for them before TMEM is freed.
+        ptx::tc_commit<CTAS>(drain_bar);
+        const uint64_t t0 = ptx::globaltimer_ns();
+        while (!ptx::mbar_try_wait(drain_bar, 0)) {
+          if (ptx::globaltimer_ns() - t0 > 2000000ull) break;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------- epilogue
+    const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) are readable by this warp
+    const uint32_t ew = warp - 2u;
+    const uint32_t stg = staging_base + ew * Cfg::STAGING_WARP_BYTES;
+    constexpr int BOX_COLS = 128 / sizeof(TOut);  // columns in one 128-byte staged row
+    constexpr int SLICES = BOX_COLS / 32;         // 32-column TMEM slices per staged box
+    constexpr int WORDS = 32 * sizeof(TOut) / 4;  // packed words per slice per row
+    uint32_t acc = 0, acc_phase = 0, sbuf = 0;
+    bool ok = true;
+    const TOut* const cmat = static_cast<const TOut*>(p.c);
+    TOut* const dmat = static_cast<TOut*>(p.d);
+    const uint32_t tmem_empty_target =
+        (CTAS == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+    for (uint32_t t = cluster; ok && t < num_tiles; t += num_clusters) {
+      uint32_t tm, tn;
+      tile_coords(p.grid, t, tm, tn);
+      if (!detail::wait(tmem_full_bar(acc), acc_phase, ab, WAIT_EPILOGUE_TMEM_FULL, t, 0)) {
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const uint32_t row0 = tm * (128u * CTAS) + rank * 128u + quad * 32u;  // first row of this warp
+      const uint32_t row = row0 + lane;
+      const bool row_ok = row < p.m;
+      const uint32_t col_tile = tn * BN;
+      const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
+      if (row0 < p.m) {
+        for (uint32_t box = 0; box < BN / BOX_COLS; ++box) {
+          const uint32_t box_col = col_tile + box * BOX_COLS;
+          if (box_col >= p.n) break;
+          const uint32_t sb_addr = stg + sbuf * 4096u;
+          if (p.epilogue_tma) {
+            // The buffer about to be overwritten was handed to a TMA store two boxes ago.
+            if (lane == 0) ptx::bulk_wait_group_read<1>();
+            __syncwarp();
+          }
+#pragma unroll
+          for (int sl = 0; sl < SLICES; ++sl) {
+            const uint32_t col0 = box_col + sl * 32u;
+            if (col0 >= p.n) break;  // uniform across the warp
+            const uint32_t ncols = (p.n - col0 < 32u) ? (p.n - col0) : 32u;
+            uint32_t v[32];
+            ptx::tmem_ld_32x32(taddr + box * BOX_COLS + sl * 32u, v);
+            ptx::tmem_wait_ld();
+            const TOut* crow = cmat + static_cast<int64_t>(row) * p.ldc + col0;
+            detail::epilogue_math<TOut>(v, p, crow, row_ok, ncols);
+            if (p.epilogue_tma) {
+              // Row `lane` of the staged box; 16-byte chunk j lands at j ^ (lane % 8),
+              // the layout a 128B-swizzled tensor map expects.
+#pragma unroll
+              for (int q = 0; q < WORDS / 4; ++q) {
+                const uint32_t j = static_cast<uint32_t>(sl * (WORDS / 4) + q);
+                const uint32_t addr = sb_addr + lane * 128u + ((j ^ (lane & 7u)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v[4 * q]),
+                             "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
+                             : "memory");
+              }
+            } else if (row_ok) {
+              TOut* drow = dmat + static_cast<int64_t>(row) * p.ldd + col0;
+              detail::store_direct<TOut>(v, drow, ncols, p.d_vec_ok != 0u);
+            }
+          }
+          if (p.epilogue_tma) {
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_2d(&tm_d, sb_addr, static_cast<int32_t>(box_col),
+                                static_cast<int32_t>(row0));
+              ptx::bulk_commit_group();
+            }
+            sbuf ^= 1u;
+          }
+        }
+      }
+      // This accumulator may now be overwritten by the MMA warp.
+      ptx::tc_fence_before_sync();
+      if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(tmem_empty_target + 8u * acc);
+      else ptx::mbar_arrive(tmem_empty_target + 8u * acc);
+      acc ^= 1u;
+      if (acc == 0u) acc_phase ^= 1u;
+    }
+    if (p.epilogue_tma && lane == 0) ptx::bulk_wait_group<0>();
+  }
+
+  // -------------------------------------------------------------- teardown
+  __syncwarp();
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (detail::aborted(ab)) {
+    // Loads issued by a peer CTA's producer are counted on the leader's
+    // barriers; give anything still in flight time to land.
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 100000ull) __nanosleep(1000);
+  }
+  if constexpr (CTAS == 2) {
+    // Neither CTA may exit (or free TMEM) while its partner can still signal
+    // its barriers or read its shared memory.
+    ptx::cluster_arrive_release();
+    ptx::cluster_wait_acquire();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace gz
+#endif

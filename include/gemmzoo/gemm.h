@@ -1,0 +1,180 @@
+/*
+ * gemmzoo C ABI — dense GEMM  D = alpha * A * B + beta * C  on NVIDIA B200 (sm_100a).
+ *
+ * This is the launch layer that sits under the C++ functor
+ * nvidia::kernel_functors::sm100_gemm (nvidia/kernel_functors/sm100_gemm.cuh).
+ * It replaces, for the reference project AD2605/gemm-zoo, what its header-only
+ * functors do inline:
+ *   - constructor of a functor (geometry, shared-memory opt-in)
+ *       nvidia/kernel_functors/bf16_mma_gemm.cuh:17-49
+ *       nvidia/kernel_functors/fp16_mma_gemm.cuh:17-47
+ *       nvidia/kernel_functors/tf32_mma_gemm.cuh:16-41
+ *       nvidia/kernel_functors/generic_gemm.cuh:15-24      -> gz_gemm_plan_create
+ *   - operator() of a functor (one asynchronous launch on a stream)
+ *       nvidia/kernel_functors/bf16_mma_gemm.cuh:51-63
+ *       nvidia/kernel_functors/generic_gemm.cuh:26-35      -> gz_gemm_run
+ *   - the s8*s8->s32 contract of intel/xe_gemm_s8_s8_s32_m8k16.hpp:27-40
+ *       (int32 alpha/beta, int32 C/D)                      -> GZ_DT_S8 / GZ_DT_S32
+ *   - the fill of operand buffers, nvidia/utils/fill_data.cuh:33-49
+ *                                                          -> gz_fill
+ *
+ * Conventions
+ *   - All pointers given to gz_gemm_run are DEVICE pointers owned by the caller.
+ *     gz_gemm_run_host takes HOST pointers and performs the copies itself.
+ *   - C and D are row-major (ldc, ldd = elements between rows), as everywhere in
+ *     the reference.  A is M x K, B is K x N; each may be row- or column-major.
+ *     Reference default: A row-major lda=K, B row-major ldb=N, C/D ld=N
+ *     (nvidia/kernels/naive_gemm.cuh:18-20).
+ *   - alpha and beta are passed by HOST pointer in the scale type of the
+ *     problem: float for f16/bf16/f32 inputs, int32_t for s8 inputs.
+ *   - C is not read when beta == 0 (the rule of nvidia/kernels/generic_gemm.cuh:55).
+ *     D may alias C.
+ *   - Nothing here exits the process or throws; every entry point returns a
+ *     gz_status.  There is no CPU fallback: without a usable sm_100 device
+ *     plan creation fails with GZ_ERR_NO_DEVICE.
+ */
+#ifndef GEMMZOO_GEMM_H
+#define GEMMZOO_GEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define GZ_API
+#else
+#define GZ_API __attribute__((visibility("default")))
+#endif
+
+typedef enum gz_status {
+  GZ_OK = 0,
+  GZ_ERR_INVALID_ARG = 1,    /* null pointer, non-positive extent, ld < extent, bad enum */
+  GZ_ERR_UNSUPPORTED = 2,    /* dtype pair / config not implemented */
+  GZ_ERR_MISALIGNED = 3,     /* pointer not aligned to its element size */
+  GZ_ERR_CUDA = 4,           /* a CUDA runtime/driver call failed; see gz_last_cuda_error */
+  GZ_ERR_DEVICE_TIMEOUT = 5, /* a bounded wait inside the kernel expired */
+  GZ_ERR_NO_DEVICE = 6,      /* no CUDA device, or device is not compute capability 10.x */
+  GZ_ERR_TOO_LARGE = 7,      /* extent exceeds what the kernel's 32-bit tile coordinates hold */
+  GZ_ERR_OUT_OF_MEMORY = 8
+} gz_status;
+
+typedef enum gz_dtype {
+  GZ_DT_F16 = 0,
+  GZ_DT_BF16 = 1,
+  GZ_DT_F32 = 2, /* as an input type: fp32 storage, tf32 multiply, fp32 accumulate */
+  GZ_DT_S8 = 3,
+  GZ_DT_S32 = 4
+} gz_dtype;
+
+typedef enum gz_layout { GZ_ROW_MAJOR = 0, GZ_COL_MAJOR = 1 } gz_layout;
+
+/* Kernel configuration.  GZ_CFG_AUTO lets the plan choose.  The explicit values
+ * exist so that tests and benchmarks can pin one variant. */
+typedef enum gz_config {
+  GZ_CFG_AUTO = 0,
+  GZ_CFG_1CTA_N256 = 1, /* 128x256 tile, one CTA */
+  GZ_CFG_1CTA_N128 = 2, /* 128x128 tile, one CTA */
+  GZ_CFG_1CTA_N64 = 3,  /* 128x64 tile, one CTA  */
+  GZ_CFG_2CTA_N256 = 4, /* 256x256 tile on a 2-CTA pair (tcgen05 cta_group::2) */
+  GZ_CFG_2CTA_N128 = 5, /* 256x128 tile on a 2-CTA pair */
+  GZ_CFG_SIMT = 15      /* plain CUDA-core kernel; chosen automatically when TMA alignment rules fail */
+} gz_config;
+
+/* flags */
+#define GZ_FLAG_EPILOGUE_DIRECT 0x1u /* registers -> global stores, no TMA store */
+#define GZ_FLAG_EPILOGUE_TMA 0x2u    /* force the shared-memory + TMA-store epilogue */
+/* Test knob: the MMA warp never signals "accumulator ready", so the epilogue's
+ * bounded wait expires and the launch reports GZ_ERR_DEVICE_TIMEOUT.  Nothing
+ * faults or hangs; use with a small wait_limit_ns. */
+#define GZ_FLAG_TEST_WITHHOLD_ACC_READY 0x80000000u
+
+typedef struct gz_gemm_desc {
+  uint32_t struct_size; /* = sizeof(gz_gemm_desc) */
+  int32_t in_type;      /* gz_dtype of A and B */
+  int32_t out_type;     /* gz_dtype of C and D */
+  int32_t layout_a;     /* gz_layout */
+  int32_t layout_b;     /* gz_layout */
+  int32_t device;       /* CUDA device ordinal */
+  int32_t config;       /* gz_config */
+  uint32_t flags;
+  int64_t m, n, k;
+  int64_t lda, ldb, ldc, ldd; /* 0 = packed default for the layout */
+  uint64_t wait_limit_ns;     /* 0 = default (2 s); bound on every in-kernel wait */
+} gz_gemm_desc;
+
+typedef struct gz_plan gz_plan;
+
+/* What the plan decided; filled by gz_gemm_plan_info. */
+typedef struct gz_plan_info {
+  int32_t config;       /* gz_config actually used */
+  int32_t tile_m, tile_n, tile_k;
+  int32_t stages;
+  int32_t ctas_per_tile;
+  int32_t grid;         /* CTAs launched */
+  int32_t smem_bytes;   /* dynamic shared memory per CTA */
+  int32_t epilogue_tma; /* 1 if the TMA-store epilogue is used */
+  int32_t sm_count;
+  int64_t tiles;        /* output tiles */
+  int64_t lda, ldb, ldc, ldd;
+} gz_plan_info;
+
+/* Host-only validation of a descriptor: every argument error is reachable
+ * without a GPU.  On success *cfg (if non-null) receives the configuration
+ * that would be chosen for a device with sm_count SMs (0 = assume 148). */
+GZ_API gz_status gz_gemm_desc_validate(const gz_gemm_desc* desc, int sm_count, gz_plan_info* info);
+
+GZ_API gz_status gz_gemm_plan_create(gz_plan** plan, const gz_gemm_desc* desc);
+GZ_API gz_status gz_gemm_plan_destroy(gz_plan* plan);
+GZ_API gz_status gz_gemm_plan_info(const gz_plan* plan, gz_plan_info* info);
+
+/* Asynchronous on `stream` (a cudaStream_t passed as void*; NULL = legacy default stream).
+ * a, b, c, d: device pointers.  c may be NULL when *beta == 0. */
+GZ_API gz_status gz_gemm_run(gz_plan* plan, const void* a, const void* b, const void* c, void* d,
+                             const void* alpha, const void* beta, void* stream);
+
+/* Same computation with HOST operands: copies A, B (and C when beta != 0) to
+ * device staging owned by the plan, runs, copies D back, and synchronises the
+ * stream before returning. */
+GZ_API gz_status gz_gemm_run_host(gz_plan* plan, const void* a, const void* b, const void* c, void* d,
+                                  const void* alpha, const void* beta, void* stream);
+
+/* Synchronises the plan's device status word: returns GZ_OK, or
+ * GZ_ERR_DEVICE_TIMEOUT if a bounded wait expired in any launch since the last
+ * call (detail[0] = role/barrier code, detail[1] = block, detail[2] = tile,
+ * detail[3] = k-block; may be NULL).  Blocks until `stream` is idle. */
+GZ_API gz_status gz_last_device_status(gz_plan* plan, void* stream, uint32_t detail[4]);
+
+GZ_API const char* gz_status_string(gz_status s);
+/* Text of the last CUDA error seen by this thread inside the library. */
+GZ_API const char* gz_last_cuda_error(void);
+
+/* Seeded synthetic operands (replaces nvidia/utils/fill_data.cuh:33-49, which
+ * needs 48 bytes of generator state per element).  Element i of a buffer gets a
+ * value that depends only on (seed, stream_id, i):
+ *   dist 0: uniform in [-1, 1)         (scale multiplies it)
+ *   dist 1: normal(0, 1) * scale
+ *   dist 2: uniform integers in [-128, 127] (s8) or [-scale, scale] rounded (others)
+ * Values are rounded to `dtype` once.  `ptr` is a device pointer. */
+GZ_API gz_status gz_fill(void* ptr, int32_t dtype, int64_t count, uint64_t seed, uint32_t stream_id,
+                         int32_t dist, float scale, void* stream);
+
+/* Tile-order function of the persistent scheduler, exposed for host tests:
+ * linear tile index t -> (tile_m, tile_n) for a tiles_m x tiles_n grid with
+ * row-group size group_m. */
+GZ_API void gz_tile_coords(uint32_t tiles_m, uint32_t tiles_n, uint32_t group_m, uint32_t t,
+                           uint32_t* tile_m, uint32_t* tile_n);
+
+/* Column partition of N over `parts` devices: part p owns [*begin, *end).
+ * Boundaries are multiples of `align` columns except the last. */
+GZ_API gz_status gz_partition_columns(int64_t n, int32_t parts, int32_t p, int64_t align,
+                                      int64_t* begin, int64_t* end);
+
+GZ_API int32_t gz_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEMMZOO_GEMM_H */
