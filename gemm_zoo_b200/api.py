@@ -22,6 +22,7 @@ GZ_ERR_DEVICE_TIMEOUT, GZ_ERR_NO_DEVICE, GZ_ERR_TOO_LARGE, GZ_ERR_OUT_OF_MEMORY 
 # Every symbol include/gemmzoo/gemm.h declares.
 EXPORTED_SYMBOLS = [
     "gz_gemm_desc_validate", "gz_gemm_plan_create", "gz_gemm_plan_destroy", "gz_gemm_plan_info",
+    "gz_gemm_plan_set_profile",
     "gz_gemm_run", "gz_gemm_run_host", "gz_last_device_status", "gz_status_string",
     "gz_last_cuda_error", "gz_fill", "gz_tile_coords", "gz_partition_columns", "gz_version",
 ]
@@ -101,6 +102,8 @@ def lib():
     L.gz_gemm_plan_info.restype = C.c_int
     L.gz_gemm_run.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp]
     L.gz_gemm_run.restype = C.c_int
+    L.gz_gemm_plan_set_profile.argtypes = [vp, vp]
+    L.gz_gemm_plan_set_profile.restype = C.c_int
     L.gz_gemm_run_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp]
     L.gz_gemm_run_host.restype = C.c_int
     L.gz_last_device_status.argtypes = [vp, vp, C.POINTER(u32 * 4)]
@@ -202,6 +205,12 @@ class Plan:
                                     C.byref(be), _stream_handle(stream))
         if st != GZ_OK:
             raise GzError(st, "gz_gemm_run_host")
+
+    def set_profile(self, buf):
+        """buf: torch int64 CUDA tensor of 8 * info().grid words, or None."""
+        st = lib().gz_gemm_plan_set_profile(self._h, _ptr(buf))
+        if st != GZ_OK:
+            raise GzError(st, "gz_gemm_plan_set_profile")
 
     def device_status(self, stream=None):
         """(status, detail[4]) after synchronising `stream`."""

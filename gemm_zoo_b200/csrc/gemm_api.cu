@@ -13,6 +13,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -203,13 +204,13 @@ using LaunchFn = cudaError_t (*)(const CUtensorMap&, const CUtensorMap&, const C
                                  const gz::GemmParams&, int grid, cudaStream_t);
 using AttrFn = cudaError_t (*)();
 
-template <class Cfg>
+template <class Cfg, bool PROF = false>
 cudaError_t set_attr() {
-  return cudaFuncSetAttribute(gz::sm100_gemm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              Cfg::SMEM_BYTES);
+  return cudaFuncSetAttribute(gz::sm100_gemm_kernel<Cfg, PROF>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
 }
 
-template <class Cfg>
+template <class Cfg, bool PROF = false>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
                    const gz::GemmParams& p, int grid, cudaStream_t stream) {
   cudaLaunchConfig_t cfg;
@@ -225,50 +226,60 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gz::sm100_gemm_kernel<Cfg>, ta, tb, td, p);
+  return cudaLaunchKernelEx(&cfg, gz::sm100_gemm_kernel<Cfg, PROF>, ta, tb, td, p);
 }
 
 struct KernelEntry {
   LaunchFn launch;
   AttrFn attr;
+  LaunchFn launch_prof;  // same kernel with stall counters compiled in (may be null)
+  AttrFn attr_prof;
 };
 
-template <gz::ptx::Kind KIND, typename TOut>
+template <class C, bool WITH_PROF>
+KernelEntry make_entry() {
+  if constexpr (WITH_PROF) return {launch<C>, set_attr<C>, launch<C, true>, set_attr<C, true>};
+  else return {launch<C>, set_attr<C>, nullptr, nullptr};
+}
+
+// Stall-counter variants are compiled for the bf16/fp16 -> 16-bit kernels only.
+template <gz::ptx::Kind KIND, typename TOut, bool WITH_PROF = false>
 KernelEntry entry_for_shape(int config) {
   switch (config) {
     case GZ_CFG_2CTA_N256: {
       using C = gz::GemmCfg<KIND, TOut, 256, 2, 6>;
-      return {launch<C>, set_attr<C>};
+      return make_entry<C, WITH_PROF>();
     }
     case GZ_CFG_1CTA_N256: {
       using C = gz::GemmCfg<KIND, TOut, 256, 1, 4>;
-      return {launch<C>, set_attr<C>};
+      return make_entry<C, WITH_PROF>();
     }
     case GZ_CFG_2CTA_N128: {
       using C = gz::GemmCfg<KIND, TOut, 128, 2, 8>;
-      return {launch<C>, set_attr<C>};
+      return make_entry<C, WITH_PROF>();
     }
     case GZ_CFG_1CTA_N128: {
       using C = gz::GemmCfg<KIND, TOut, 128, 1, 6>;
-      return {launch<C>, set_attr<C>};
+      return make_entry<C, WITH_PROF>();
     }
     case GZ_CFG_1CTA_N64: {
       using C = gz::GemmCfg<KIND, TOut, 64, 1, 8>;
-      return {launch<C>, set_attr<C>};
+      return make_entry<C, WITH_PROF>();
     }
   }
-  return {nullptr, nullptr};
+  return {nullptr, nullptr, nullptr, nullptr};
 }
 
 KernelEntry entry_for(int in, int out, int config) {
   using gz::ptx::Kind;
   if (in == GZ_DT_F16 && out == GZ_DT_F16) return entry_for_shape<Kind::F16, __half>(config);
-  if (in == GZ_DT_BF16 && out == GZ_DT_BF16) return entry_for_shape<Kind::F16, __nv_bfloat16>(config);
+  if (in == GZ_DT_BF16 && out == GZ_DT_BF16)
+    return entry_for_shape<Kind::F16, __nv_bfloat16, true>(config);
   if ((in == GZ_DT_F16 || in == GZ_DT_BF16) && out == GZ_DT_F32)
     return entry_for_shape<Kind::F16, float>(config);
   if (in == GZ_DT_F32) return entry_for_shape<Kind::TF32, float>(config);
   if (in == GZ_DT_S8) return entry_for_shape<Kind::I8, int32_t>(config);
-  return {nullptr, nullptr};
+  return {nullptr, nullptr, nullptr, nullptr};
 }
 
 template <typename TIn, typename TOut>
@@ -301,7 +312,8 @@ CUtensorMapDataType tmap_type(int dt) {
 
 // 2-D tensor map: dim0 (contiguous) x dim1, row pitch `pitch_bytes`, 128-byte swizzle.
 bool encode_2d(CUtensorMap* tm, int dt, const void* base, uint64_t dim0, uint64_t dim1,
-               uint64_t pitch_bytes, uint32_t box0, uint32_t box1, bool promote) {
+               uint64_t pitch_bytes, uint32_t box0, uint32_t box1, bool promote,
+               bool swizzle_32b_atom = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) {
     g_last_cuda_error = "cuTensorMapEncodeTiled entry point not available";
@@ -312,7 +324,8 @@ bool encode_2d(CUtensorMap* tm, int dt, const void* base, uint64_t dim0, uint64_
   cuuint32_t box[2] = {box0, box1};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(tm, tmap_type(dt), 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle_32b_atom ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                   promote ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -361,6 +374,13 @@ void build_operand(gz::OperandDesc* od, bool mn_major, int rows, int in_size) {
     od->desc_lo = ((od->box_bytes >> 4) & 0x3FFFu) << 16;  // distance between M/N chunks
     const int umma_k = 32 / in_size;
     od->k_step16 = (uint32_t)(umma_k * 128) >> 4;
+    if (in_size == 4) {
+      // 32-bit elements with M/N contiguous exist only in the "128-byte swizzle,
+      // 32-byte atom" layout: 32-byte chunks are permuted over groups of 4 K-rows
+      // (TMA: SWIZZLE_128B_ATOM_32B), and the descriptor strides over 4-row groups.
+      od->desc_hi = (512u >> 4) | (1u << 14) | (1u << 29);
+      return;
+    }
   }
   od->desc_hi = sbo | (1u << 14) /* descriptor version for sm_100 */ | (2u << 29) /* 128B swizzle */;
 }
@@ -410,7 +430,9 @@ GZ_API const char* gz_status_string(gz_status s) {
     case GZ_OK: return "ok";
     case GZ_ERR_INVALID_ARG: return "invalid argument";
     case GZ_ERR_UNSUPPORTED: return "unsupported data type combination or configuration";
-    case GZ_ERR_MISALIGNED: return "pointer is not aligned to its element size";
+    case GZ_ERR_MISALIGNED:
+      return "operand violates an alignment rule (element alignment, or 16-byte leading dimension for "
+             "an explicitly requested tensor-core configuration)";
     case GZ_ERR_CUDA: return "CUDA call failed";
     case GZ_ERR_DEVICE_TIMEOUT: return "a bounded wait inside the kernel expired";
     case GZ_ERR_NO_DEVICE: return "no CUDA device of compute capability 10.x";
@@ -494,7 +516,7 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
   pl->ha_bytes = pl->hb_bytes = pl->hcd_bytes = 0;
   fill_info(pr, config, sm_count, &pl->info);
   std::memset(&pl->base, 0, sizeof(pl->base));
-  pl->entry = {nullptr, nullptr};
+  pl->entry = {nullptr, nullptr, nullptr, nullptr};
 
   if (!cuda_ok(cudaMalloc(&pl->status_dev, 4 * sizeof(uint32_t)), "cudaMalloc(status)") ||
       !cuda_ok(cudaMemset(pl->status_dev, 0, 4 * sizeof(uint32_t)), "cudaMemset(status)")) {
@@ -534,6 +556,12 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
     p.idesc = build_idesc(pr, s);
     p.epilogue_tma = pl->info.epilogue_tma;
     p.test_flags = (pr.d.flags & 0x80000000u) ? 1u : 0u;
+    // Developer tuning knobs, read once per plan.
+    if (const char* e = std::getenv("GZ_TUNE")) p.tune = (uint32_t)std::strtoul(e, nullptr, 0);
+    if (const char* e = std::getenv("GZ_TUNE_GROUP_M")) {
+      const long g = std::strtol(e, nullptr, 0);
+      if (g > 0) p.grid.group_m = (uint32_t)g;
+    }
     p.ldc = pr.d.ldc;
     p.ldd = pr.d.ldd;
     p.status = pl->status_dev;
@@ -552,6 +580,18 @@ GZ_API gz_status gz_gemm_plan_destroy(gz_plan* pl) {
   if (pl->hc) cudaFree(pl->hc);
   if (pl->hd) cudaFree(pl->hd);
   delete pl;
+  return GZ_OK;
+}
+
+GZ_API gz_status gz_gemm_plan_set_profile(gz_plan* pl, void* device_words) {
+  if (!pl) return GZ_ERR_INVALID_ARG;
+  if (device_words) {
+    if (!pl->entry.launch_prof) return GZ_ERR_UNSUPPORTED;
+    if (!cuda_ok(cudaSetDevice(pl->pr.d.device), "cudaSetDevice") ||
+        !cuda_ok(pl->entry.attr_prof(), "cudaFuncSetAttribute(max dynamic shared memory)"))
+      return GZ_ERR_CUDA;
+  }
+  pl->base.prof = static_cast<unsigned long long*>(device_words);
   return GZ_OK;
 }
 
@@ -627,14 +667,14 @@ GZ_API gz_status gz_gemm_run(gz_plan* pl, const void* a, const void* b, const vo
                    (uint64_t)pr.d.lda * pr.in_size, bk, 128, true);
   else
     ok = encode_2d(&ta, pr.d.in_type, a, (uint64_t)pr.d.m, (uint64_t)pr.d.k,
-                   (uint64_t)pr.d.lda * pr.in_size, p.a.box_mn, bk, true);
+                   (uint64_t)pr.d.lda * pr.in_size, p.a.box_mn, bk, true, pr.in_size == 4);
   if (!ok) return GZ_ERR_CUDA;
   if (!pr.b_mn_major)
     ok = encode_2d(&tb, pr.d.in_type, b, (uint64_t)pr.d.k, (uint64_t)pr.d.n,
                    (uint64_t)pr.d.ldb * pr.in_size, bk, (uint32_t)(s.bn / s.ctas), true);
   else
     ok = encode_2d(&tb, pr.d.in_type, b, (uint64_t)pr.d.n, (uint64_t)pr.d.k,
-                   (uint64_t)pr.d.ldb * pr.in_size, p.b.box_mn, bk, true);
+                   (uint64_t)pr.d.ldb * pr.in_size, p.b.box_mn, bk, true, pr.in_size == 4);
   if (!ok) return GZ_ERR_CUDA;
   if (p.epilogue_tma) {
     ok = encode_2d(&td, pr.d.out_type, d, (uint64_t)pr.d.n, (uint64_t)pr.d.m,
@@ -643,7 +683,8 @@ GZ_API gz_status gz_gemm_run(gz_plan* pl, const void* a, const void* b, const vo
   } else {
     td = ta;  // unused by the kernel in this mode
   }
-  if (!cuda_ok(pl->entry.launch(ta, tb, td, p, pl->info.grid, stream), "kernel launch"))
+  const LaunchFn fn = p.prof ? pl->entry.launch_prof : pl->entry.launch;
+  if (!cuda_ok(fn(ta, tb, td, p, pl->info.grid, stream), "kernel launch"))
     return GZ_ERR_CUDA;
   return GZ_OK;
 }

@@ -20,6 +20,19 @@ __device__ __forceinline__ uint32_t lane_id() {
   return r;
 }
 
+// True in exactly one lane of a fully active warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -139,6 +152,14 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
       : "memory");
 }
 
+// Bring a 2-D tile into L2 only (no shared-memory destination, no barrier).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int32_t c0, int32_t c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1)
+               : "memory");
+}
+
 // 2-D tile store shared -> global (bulk async-group completion).
 __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int32_t c0,
                                              int32_t c1) {
@@ -219,6 +240,17 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                      bar)
                  : "memory");
   }
+}
+
+// 2-CTA pair only: one commit that arrives on the barrier at the same offset in
+// both CTAs of the pair (CTA mask 0b11).
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          bar),
+      "h"(mask)
+      : "memory");
 }
 
 enum class Kind : int { F16 = 0, TF32 = 1, I8 = 2 };

@@ -8,9 +8,10 @@
 // (persistent CTAs, multi-stage operand ring, fused alpha/beta epilogue,
 // next tile's loads overlapping this tile's epilogue), different machinery:
 //
-//   warp 0      one lane issues TMA tile loads (128-byte-swizzled boxes) into a
-//               STAGES-deep shared-memory ring; completion is counted in bytes
-//               on the stage's "full" mbarrier.
+//   warps 0, 6  one lane of each issues TMA tile loads (128-byte-swizzled boxes;
+//               warp 0 the A tile, warp 6 the B tile) into a STAGES-deep
+//               shared-memory ring; completion is counted in bytes on the
+//               stage's "full" mbarrier.
 //   warp 1      allocates TMEM; one lane (of the leader CTA when two CTAs share
 //               a tile) issues tcgen05.mma from shared-memory descriptors into
 //               one of two TMEM accumulators and commits each stage back to its
@@ -80,6 +81,22 @@ struct GemmParams {
   void* d;
   uint32_t* status;  // 4 words in global memory
   uint64_t wait_limit_ns;
+  // Tuning switches (see TUNE_* below).
+  uint32_t tune;
+  // Optional stall counters, 16 words per CTA (null = off):
+  //  [0] A producer: clocks waiting for a free stage   [1] A producer: total clocks
+  //  [2] MMA: clocks waiting for operand data          [3] MMA: clocks waiting for a free accumulator
+  //  [4] MMA: total clocks                             [5] epilogue warp 2: clocks waiting for an accumulator
+  //  [6] epilogue warp 2: total clocks                 [7] MMA: elapsed nanoseconds (globaltimer)
+  //  [8] A producer: clocks issuing copies               [9] MMA: clocks issuing MMAs and commits
+  //  [10] B producer: clocks waiting for a free stage   [11] B producer: clocks issuing copies
+  // Only kernels instantiated with PROF = true write them.
+  unsigned long long* prof;
+};
+
+enum : uint32_t {
+  TUNE_COMMIT_MULTICAST = 1u,  // 2-CTA tiles: one multicast commit instead of two plain commits
+  TUNE_L2_PREFETCH_SHIFT = 8,  // bits 8..15: prefetch operand tiles into L2 this many K blocks ahead
 };
 
 template <ptx::Kind KIND_, typename TOut_, int BN_, int CTAS_, int STAGES_>
@@ -98,7 +115,7 @@ struct GemmCfg {
   static constexpr int STAGING_BYTES = 4 * STAGING_WARP_BYTES;
   static constexpr int BAR_BYTES = 256;
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators
-  static constexpr int THREADS = 192;
+  static constexpr int THREADS = 224;  // 2 producer warps, 1 MMA warp, 4 epilogue warps
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile N");
   static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
@@ -140,13 +157,19 @@ __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, const Abort&
     else return ptx::mbar_try_wait(bar, parity);
   };
   if (poll()) return true;
-  const uint64_t t0 = ptx::globaltimer_ns();
+  // Slow path.  The timer is read only every 256 failed polls (each poll may
+  // itself sleep for a hardware-defined slice), so the common short wait costs
+  // nothing but polls; the limit counts from the first timer read.
+  uint64_t t0 = 0;
   uint32_t spins = 0;
   for (;;) {
     if (poll()) return true;
-    if ((++spins & 31u) == 0u) {
+    if ((++spins & 255u) == 0u) {
       if (aborted(ab)) return false;
-      if (ptx::globaltimer_ns() - t0 > ab.limit_ns) {
+      const uint64_t now = ptx::globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > ab.limit_ns) {
         record_timeout(ab, code, tile, kb);
         return false;
       }
@@ -285,7 +308,7 @@ __device__ __forceinline__ void store_direct(const uint32_t (&v)[32], TOut* drow
 
 }  // namespace detail
 
-template <class Cfg>
+template <class Cfg, bool PROF = false>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_d, const GemmParams p) {
@@ -322,7 +345,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (threadIdx.x == 0) {
     *abort_flag = 0u;
     for (uint32_t s = 0; s < STAGES; ++s) {
-      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(full_bar(s), 2);  // one arrive.expect_tx per producer warp
       ptx::mbar_init(empty_bar(s), 1);
     }
     for (uint32_t b = 0; b < 2; ++b) {
@@ -351,122 +374,182 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const uint32_t k_blocks = p.k_blocks;
   const uint32_t num_tiles = p.grid.num_tiles;
 
-  if (warp == 0) {
-    // ---------------------------------------------------------- TMA producer
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
-      bool ok = true;
-      for (uint32_t t = cluster; ok && t < num_tiles; t += num_clusters) {
-        uint32_t tm, tn;
-        tile_coords(p.grid, t, tm, tn);
-        const int32_t row_a = static_cast<int32_t>(tm * (128u * CTAS) + rank * 128u);
-        const int32_t row_b = static_cast<int32_t>(tn * BN + rank * Cfg::BN_CTA);
-        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-          if (!detail::wait(empty_bar(stage), phase ^ 1u, ab, WAIT_PRODUCER_EMPTY, t, kb)) {
-            ok = false;
-            break;
-          }
-          const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
-          const uint32_t sb = sa + Cfg::A_BYTES;
-          const int32_t k0 = static_cast<int32_t>(kb * p.bk);
+  if (warp == 0 || warp == 6) {
+    // ---------------------------------------------------------- TMA producers
+    // Two producer warps, one per operand (warp 0: A, warp 6: B), because the
+    // issue cost of a tensor copy is per instruction: split across two
+    // instruction streams, neither limits the main loop.  Each whole warp walks
+    // the loop (loop state stays warp-uniform); one elected lane issues.
+    const bool is_b = warp == 6;
+    const OperandDesc& od = is_b ? p.b : p.a;
+    const void* const tmap = is_b ? static_cast<const void*>(&tm_b) : static_cast<const void*>(&tm_a);
+    const uint32_t boxes = od.boxes, box_bytes = od.box_bytes, box_mn = od.box_mn;
+    const bool mn_major = od.mn_major != 0u;
+    const uint32_t my_bytes = is_b ? Cfg::B_BYTES : Cfg::A_BYTES;
+    const uint32_t smem_off = is_b ? Cfg::A_BYTES : 0u;
+    const uint32_t bk = p.bk;
+    const uint32_t l2_dist = (p.tune >> TUNE_L2_PREFETCH_SHIFT) & 0xFFu;
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    long long prof_wait = 0, prof_issue = 0;
+    const long long prof_t0 = PROF ? clock64() : 0;
+    for (uint32_t t = cluster; ok && t < num_tiles; t += num_clusters) {
+      uint32_t tm, tn;
+      tile_coords(p.grid, t, tm, tn);
+      const int32_t row0 = is_b ? static_cast<int32_t>(tn * BN + rank * Cfg::BN_CTA)
+                                : static_cast<int32_t>(tm * (128u * CTAS) + rank * 128u);
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        const long long w0 = PROF ? clock64() : 0;
+        const bool got = detail::wait(empty_bar(stage), phase ^ 1u, ab, WAIT_PRODUCER_EMPTY, t, kb);
+        ok = __all_sync(0xFFFFFFFFu, got);
+        if (!ok) break;
+        const long long w1 = PROF ? clock64() : 0;
+        if constexpr (PROF) prof_wait += w1 - w0;
+        if (ptx::elect_one()) {
+          const uint32_t dst = base + stage * Cfg::STAGE_BYTES + smem_off;
+          const int32_t k0 = static_cast<int32_t>(kb * bk);
+          uint32_t fb;
           if constexpr (CTAS == 1) {
-            const uint32_t fb = full_bar(stage);
-            ptx::mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
-            for (uint32_t i = 0; i < p.a.boxes; ++i) {
-              const int32_t mn = row_a + static_cast<int32_t>(i * p.a.box_mn);
-              ptx::tma_load_2d(sa + i * p.a.box_bytes, &tm_a, p.a.mn_major ? mn : k0,
-                               p.a.mn_major ? k0 : mn, fb);
-            }
-            for (uint32_t i = 0; i < p.b.boxes; ++i) {
-              const int32_t mn = row_b + static_cast<int32_t>(i * p.b.box_mn);
-              ptx::tma_load_2d(sb + i * p.b.box_bytes, &tm_b, p.b.mn_major ? mn : k0,
-                               p.b.mn_major ? k0 : mn, fb);
-            }
+            fb = full_bar(stage);
+            ptx::mbar_arrive_expect_tx(fb, my_bytes);
           } else {
             // Both CTAs' bytes are counted on the leader's barrier.
-            const uint32_t fb = ptx::mapa(full_bar(stage), 0);
-            if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
-            for (uint32_t i = 0; i < p.a.boxes; ++i) {
-              const int32_t mn = row_a + static_cast<int32_t>(i * p.a.box_mn);
-              ptx::tma_load_2d_pair(sa + i * p.a.box_bytes, &tm_a, p.a.mn_major ? mn : k0,
-                                    p.a.mn_major ? k0 : mn, fb);
-            }
-            for (uint32_t i = 0; i < p.b.boxes; ++i) {
-              const int32_t mn = row_b + static_cast<int32_t>(i * p.b.box_mn);
-              ptx::tma_load_2d_pair(sb + i * p.b.box_bytes, &tm_b, p.b.mn_major ? mn : k0,
-                                    p.b.mn_major ? k0 : mn, fb);
-            }
+            fb = ptx::mapa(full_bar(stage), 0);
+            if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2u * my_bytes);
           }
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
+          for (uint32_t i = 0; i < boxes; ++i) {
+            const int32_t mn = row0 + static_cast<int32_t>(i * box_mn);
+            if constexpr (CTAS == 1)
+              ptx::tma_load_2d(dst + i * box_bytes, tmap, mn_major ? mn : k0, mn_major ? k0 : mn, fb);
+            else
+              ptx::tma_load_2d_pair(dst + i * box_bytes, tmap, mn_major ? mn : k0, mn_major ? k0 : mn, fb);
+          }
+          if (l2_dist != 0u && kb + l2_dist < k_blocks) {
+            const int32_t kp = static_cast<int32_t>((kb + l2_dist) * bk);
+            for (uint32_t i = 0; i < boxes; ++i) {
+              const int32_t mn = row0 + static_cast<int32_t>(i * box_mn);
+              ptx::tma_prefetch_l2_2d(tmap, mn_major ? mn : kp, mn_major ? kp : mn);
+            }
           }
         }
+        __syncwarp();
+        if constexpr (PROF) prof_issue += clock64() - w1;
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
-      if (!ok && rank == 0) {
-        // Aborting: give loads already issued a bounded chance to land before
-        // the CTA's shared memory is released.  (stage, phase) is the next slot
-        // to fill; the STAGES slots before it are the ones that may be in flight.
-        const uint64_t t0 = ptx::globaltimer_ns();
-        for (uint32_t i = 0; i < STAGES; ++i) {
-          const uint32_t s = (stage + STAGES - 1u - i) % STAGES;
-          const uint32_t ph = (s < stage) ? phase : (phase ^ 1u);
-          while (!ptx::mbar_try_wait(full_bar(s), ph)) {
-            if (ptx::globaltimer_ns() - t0 > 2000000ull) break;
-          }
+    }
+    if constexpr (PROF) {
+      if (lane == 0 && p.prof) {
+        p.prof[16 * blockIdx.x + (is_b ? 10 : 0)] = prof_wait;
+        p.prof[16 * blockIdx.x + (is_b ? 11 : 8)] = prof_issue;
+        if (!is_b) p.prof[16 * blockIdx.x + 1] = clock64() - prof_t0;
+      }
+    }
+    if (!ok && rank == 0 && lane == 0) {
+      // Aborting: give loads already issued a bounded chance to land before
+      // the CTA's shared memory is released.  (stage, phase) is the next slot
+      // to fill; the STAGES slots before it are the ones that may be in flight.
+      const uint64_t t0 = ptx::globaltimer_ns();
+      for (uint32_t i = 0; i < STAGES; ++i) {
+        const uint32_t s = (stage + STAGES - 1u - i) % STAGES;
+        const uint32_t ph = (s < stage) ? phase : (phase ^ 1u);
+        while (!ptx::mbar_try_wait(full_bar(s), ph)) {
+          if (ptx::globaltimer_ns() - t0 > 2000000ull) break;
         }
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0 && rank == 0) {
+    // Only the leader CTA of a pair issues.  As in the producer, the whole warp
+    // walks the loop and one elected lane issues tcgen05.mma / tcgen05.commit.
+    if (rank == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       bool issued = false;
-      const uint64_t a_hi = static_cast<uint64_t>(p.a.desc_hi) << 32;
-      const uint64_t b_hi = static_cast<uint64_t>(p.b.desc_hi) << 32;
+      long long prof_full = 0, prof_tmem = 0, prof_issue = 0;
+      const long long prof_t0 = PROF ? clock64() : 0;
+      const uint64_t prof_ns0 = PROF ? ptx::globaltimer_ns() : 0;
+      const bool mcast = (p.tune & TUNE_COMMIT_MULTICAST) != 0u;
+      const uint32_t a_hi = p.a.desc_hi, b_hi = p.b.desc_hi;
+      const uint32_t a_lo0 = ((base >> 4) & 0x3FFFu) | p.a.desc_lo;
+      const uint32_t b_lo0 = (((base + Cfg::A_BYTES) >> 4) & 0x3FFFu) | p.b.desc_lo;
+      const uint32_t a_step = p.a.k_step16, b_step = p.b.k_step16;
+      const uint32_t idesc = p.idesc;
       for (uint32_t t = cluster; ok && t < num_tiles; t += num_clusters) {
-        if (!detail::wait<CTAS == 2>(tmem_empty_bar(acc), acc_phase ^ 1u, ab, WAIT_MMA_TMEM_EMPTY, t,
-                                     0)) {
-          ok = false;
-          break;
-        }
+        const long long w0 = PROF ? clock64() : 0;
+        const bool got0 = detail::wait<CTAS == 2>(tmem_empty_bar(acc), acc_phase ^ 1u, ab,
+                                                  WAIT_MMA_TMEM_EMPTY, t, 0);
+        ok = __all_sync(0xFFFFFFFFu, got0);
+        if (!ok) break;
+        if constexpr (PROF) prof_tmem += clock64() - w0;
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-          if (!detail::wait(full_bar(stage), phase, ab, WAIT_MMA_FULL, t, kb)) {
-            ok = false;
-            break;
-          }
+          const long long w1 = PROF ? clock64() : 0;
+          const bool got = detail::wait(full_bar(stage), phase, ab, WAIT_MMA_FULL, t, kb);
+          ok = __all_sync(0xFFFFFFFFu, got);
+          if (!ok) break;
+          const long long w2 = PROF ? clock64() : 0;
+          if constexpr (PROF) prof_full += w2 - w1;
           ptx::tc_fence_after_sync();
-          const uint32_t sa = base + stage * Cfg::STAGE_BYTES;
-          const uint32_t sb = sa + Cfg::A_BYTES;
-          const uint32_t a_lo = ((sa >> 4) & 0x3FFFu) | p.a.desc_lo;
-          const uint32_t b_lo = ((sb >> 4) & 0x3FFFu) | p.b.desc_lo;
+          if (ptx::elect_one()) {
+            const uint32_t a_lo = a_lo0 + stage * (Cfg::STAGE_BYTES >> 4);
+            const uint32_t b_lo = b_lo0 + stage * (Cfg::STAGE_BYTES >> 4);
 #pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) {  // 128 bytes of K per stage, 32 bytes per MMA
-            const uint64_t ad = a_hi | static_cast<uint64_t>(a_lo + j * p.a.k_step16);
-            const uint64_t bd = b_hi | static_cast<uint64_t>(b_lo + j * p.b.k_step16);
-            ptx::umma<Cfg::KIND, CTAS>(d_tmem, ad, bd, p.idesc, (kb | j) != 0u ? 1u : 0u);
+            for (uint32_t j = 0; j < 4; ++j) {  // 128 bytes of K per stage, 32 bytes per MMA
+              const uint64_t ad = (static_cast<uint64_t>(a_hi) << 32) | (a_lo + j * a_step);
+              const uint64_t bd = (static_cast<uint64_t>(b_hi) << 32) | (b_lo + j * b_step);
+              ptx::umma<Cfg::KIND, CTAS>(d_tmem, ad, bd, idesc, (kb | j) != 0u ? 1u : 0u);
+            }
+            // Release the stage to the producer(s) once these MMAs have read it.
+            if constexpr (CTAS == 2) {
+              if (mcast) {
+                ptx::tc_commit_pair(empty_bar(stage));
+              } else {
+                ptx::tc_commit<CTAS>(empty_bar(stage));
+                ptx::tc_commit<CTAS>(ptx::mapa(empty_bar(stage), 1));
+              }
+            } else {
+              ptx::tc_commit<CTAS>(empty_bar(stage));
+            }
           }
+          __syncwarp();
+          if constexpr (PROF) prof_issue += clock64() - w2;
           issued = true;
-          // Release the stage to the producer(s) once these MMAs have read it.
-          ptx::tc_commit<CTAS>(empty_bar(stage));
-          if constexpr (CTAS == 2) ptx::tc_commit<CTAS>(ptx::mapa(empty_bar(stage), 1));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        if (!(p.test_flags & 1u)) {
-          ptx::tc_commit<CTAS>(tmem_full_bar(acc));
-          if constexpr (CTAS == 2) ptx::tc_commit<CTAS>(ptx::mapa(tmem_full_bar(acc), 1));
+        if (!(p.test_flags & 1u) && ptx::elect_one()) {
+          if constexpr (CTAS == 2) {
+            if (mcast) {
+              ptx::tc_commit_pair(tmem_full_bar(acc));
+            } else {
+              ptx::tc_commit<CTAS>(tmem_full_bar(acc));
+              ptx::tc_commit<CTAS>(ptx::mapa(tmem_full_bar(acc), 1));
+            }
+          } else {
+            ptx::tc_commit<CTAS>(tmem_full_bar(acc));
+          }
         }
+        __syncwarp();
         acc ^= 1u;
         if (acc == 0u) acc_phase ^= 1u;
       }
-      if ((!ok || (p.test_flags & 1u)) && issued) {
+      if constexpr (PROF) {
+        if (lane == 0 && p.prof) {
+          p.prof[16 * blockIdx.x + 2] = prof_full;
+          p.prof[16 * blockIdx.x + 3] = prof_tmem;
+          p.prof[16 * blockIdx.x + 4] = clock64() - prof_t0;
+          p.prof[16 * blockIdx.x + 7] = ptx::globaltimer_ns() - prof_ns0;
+          p.prof[16 * blockIdx.x + 9] = prof_issue;
+        }
+      }
+      if ((!ok || (p.test_flags & 1u)) && issued && lane == 0) {
         // Aborting with MMAs possibly in flight: wait (bounded) for them before TMEM is freed.
         ptx::tc_commit<CTAS>(drain_bar);
         const uint64_t t0 = ptx::globaltimer_ns();
@@ -485,6 +568,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     constexpr int WORDS = 32 * sizeof(TOut) / 4;  // packed words per slice per row
     uint32_t acc = 0, acc_phase = 0, sbuf = 0;
     bool ok = true;
+    const bool prof = PROF && p.prof != nullptr && warp == 2 && lane == 0;
+    long long prof_wait = 0;
+    const long long prof_t0 = prof ? clock64() : 0;
     const TOut* const cmat = static_cast<const TOut*>(p.c);
     TOut* const dmat = static_cast<TOut*>(p.d);
     const uint32_t tmem_empty_target =
@@ -492,10 +578,12 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     for (uint32_t t = cluster; ok && t < num_tiles; t += num_clusters) {
       uint32_t tm, tn;
       tile_coords(p.grid, t, tm, tn);
+      const long long w0 = prof ? clock64() : 0;
       if (!detail::wait(tmem_full_bar(acc), acc_phase, ab, WAIT_EPILOGUE_TMEM_FULL, t, 0)) {
         ok = false;
         break;
       }
+      if (prof) prof_wait += clock64() - w0;
       ptx::tc_fence_after_sync();
       const uint32_t row0 = tm * (128u * CTAS) + rank * 128u + quad * 32u;  // first row of this warp
       const uint32_t row = row0 + lane;
@@ -558,6 +646,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       if (acc == 0u) acc_phase ^= 1u;
     }
     if (p.epilogue_tma && lane == 0) ptx::bulk_wait_group<0>();
+    if (prof) {
+      p.prof[16 * blockIdx.x + 5] = prof_wait;
+      p.prof[16 * blockIdx.x + 6] = clock64() - prof_t0;
+    }
   }
 
   // -------------------------------------------------------------- teardown

@@ -53,7 +53,8 @@ typedef enum gz_status {
   GZ_OK = 0,
   GZ_ERR_INVALID_ARG = 1,    /* null pointer, non-positive extent, ld < extent, bad enum */
   GZ_ERR_UNSUPPORTED = 2,    /* dtype pair / config not implemented */
-  GZ_ERR_MISALIGNED = 3,     /* pointer not aligned to its element size */
+  GZ_ERR_MISALIGNED = 3,     /* pointer not aligned to its element size, or an explicit tensor-core
+                                config asked for with a leading dimension that is not 16-byte sized */
   GZ_ERR_CUDA = 4,           /* a CUDA runtime/driver call failed; see gz_last_cuda_error */
   GZ_ERR_DEVICE_TIMEOUT = 5, /* a bounded wait inside the kernel expired */
   GZ_ERR_NO_DEVICE = 6,      /* no CUDA device, or device is not compute capability 10.x */
@@ -129,6 +130,13 @@ GZ_API gz_status gz_gemm_desc_validate(const gz_gemm_desc* desc, int sm_count, g
 GZ_API gz_status gz_gemm_plan_create(gz_plan** plan, const gz_gemm_desc* desc);
 GZ_API gz_status gz_gemm_plan_destroy(gz_plan* plan);
 GZ_API gz_status gz_gemm_plan_info(const gz_plan* plan, gz_plan_info* info);
+
+/* Diagnostics: give the plan a device buffer of 16 * info.grid 64-bit words and
+ * every later launch records, per CTA, the clocks its producer, MMA and epilogue
+ * roles spent waiting (layout: see GemmParams::prof in csrc/sm100_gemm.cuh).
+ * NULL switches it off again.  Counters are compiled in for bf16 -> bf16 plans only;
+ * others return GZ_ERR_UNSUPPORTED.  No counterpart in the reference. */
+GZ_API gz_status gz_gemm_plan_set_profile(gz_plan* plan, void* device_words);
 
 /* Asynchronous on `stream` (a cudaStream_t passed as void*; NULL = legacy default stream).
  * a, b, c, d: device pointers.  c may be NULL when *beta == 0. */
