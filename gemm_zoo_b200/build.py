@@ -10,7 +10,7 @@ Targets
   ref        oracle/_ref/libref_kernels.so      the reference project's own kernels, compiled
                                                  from its sources where they lie (only when
                                                  those sources are present on this machine)
-  bench      gemm_zoo_b200/nvidia/bench/*       bench mains built against the C++ functor
+  bench      gemm_zoo_b200/nvidia/bench/build/* bench mains built against the C++ functor
 """
 from __future__ import annotations
 
@@ -71,9 +71,9 @@ def build_lib(force=False, verbose=False, ptxas_info=False) -> Path:
 def build_cublaslt(force=False, verbose=False) -> Path:
     out = PKG / "libgz_cublaslt.so"
     src = PKG / "cmp" / "cublaslt_cmp.cu"
-    if force or _newer(out, [src]):
+    if force or _newer(out, [src, PKG / "nvidia" / "kernel_functors" / "cublaslt_gemm.cuh"]):
         cmd = [nvcc_path(), *ARCH, *NVCC_COMMON, "-Xcompiler", "-fPIC", "-shared", f"-I{INCLUDE}",
-               "-o", out, src, "-lcublasLt"]
+               f"-I{PKG / 'nvidia'}", "-o", out, src, "-lcublasLt"]
         _run(cmd, verbose)
     return out
 
@@ -112,8 +112,9 @@ def build_bench(force=False, verbose=False):
     outs = []
     bench_dir = PKG / "nvidia" / "bench"
     lib = build_lib(verbose=verbose)
+    (bench_dir / "build").mkdir(exist_ok=True)
     for src in sorted(bench_dir.glob("*.cu")):
-        out = bench_dir / src.stem
+        out = bench_dir / "build" / src.stem
         deps = [src, lib] + list((PKG / "nvidia").rglob("*.cuh")) + list((PKG / "nvidia").rglob("*.hpp"))
         if force or _newer(out, deps):
             cmd = [nvcc_path(), *ARCH, *NVCC_COMMON, f"-I{INCLUDE}", f"-I{PKG / 'nvidia'}", "-o", out, src,

@@ -1,0 +1,19 @@
+// Benchmark of cuBLASLt (the comparator): the dtype pair of nvidia/bench/bench_fp16_mma_gemm.cu:10-18, accumulated in fp32 instead of fp16.
+// Same shape as the reference's bench mains: pick the functor, call the harness.
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+
+#include <tuple>
+
+#include "kernel_functors/cublaslt_gemm.cuh"
+#include "kernel_functors/sm100_gemm.cuh"
+#include "utils/benchmark.cuh"
+
+int main() {
+  using TIn = __half;
+  using TOut = __half;
+  const TOut alpha = __half(1.0f);
+  const TOut beta = __half(1.0f);
+  using kernel_functor_struct = nvidia::kernel_functors::cublasLt_gemm<TIn, TOut, nvidia::kernel_functors::RowMajor, nvidia::kernel_functors::RowMajor>;
+  benchmark::benchmark<kernel_functor_struct, TIn, TOut>({{256, 256, 256}, {512, 512, 512}, {1024, 1024, 1024}, {2048, 2048, 2048}, {4096, 4096, 4096}, {8192, 8192, 8192}}, alpha, beta);
+}

@@ -57,6 +57,9 @@ inline float scalar_to_float(T v) {
 template <typename TIn, typename TOut, typename LayoutA = RowMajor, typename LayoutB = RowMajor,
           int Config = GZ_CFG_AUTO>
 struct sm100_gemm {
+  static constexpr bool a_col_major = std::is_same_v<LayoutA, ColMajor>;
+  static constexpr bool b_col_major = std::is_same_v<LayoutB, ColMajor>;
+
   sm100_gemm(std::size_t m, std::size_t n, std::size_t k, const cudaDeviceProp& properties)
       : sm100_gemm(m, n, k, 0, 0, 0, 0, properties) {}
 

@@ -1,0 +1,41 @@
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+def _has_cuda():
+    try:
+        import torch
+        return torch.cuda.is_available()
+    except Exception:
+        return False
+
+
+def pytest_collection_modifyitems(config, items):
+    if _has_cuda():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session", autouse=True)
+def _built():
+    """Build the native pieces in-tree if they are missing (staleness is handled by
+    __graft_entry__.build(), which compares time stamps)."""
+    from gemm_zoo_b200 import build as b
+    if not (b.PKG / "libgemmzoo.so").exists():
+        b.build_lib()
+    if not (b.ORACLE / "liboracle.so").exists():
+        b.build_oracle()
+    yield

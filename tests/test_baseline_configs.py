@@ -1,0 +1,89 @@
+"""The five configurations of BASELINE.json on the GPU, at full size.
+
+Full CPU comparison up to 4096^3; above that all columns of 64 seeded rows are
+compared (the same kernel computes every row the same way, and the properties in
+test_properties.py tie the rest together).  Operands are generated on the device
+with gz_fill (seeded, distinct streams per operand) and copied back for the oracle.
+
+Tolerances: s8 bit-exact; bf16/fp16 max |D-R| / max |R| <= 1e-2 (BASELINE.json) and
+the per-element bars of tests/helpers.py; tf32 |D-R| <= 2^-9 * sum|a||b|."""
+import numpy as np
+import pytest
+import torch
+
+import gemm_zoo_b200 as gz
+from oracle import cpu_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run_config(in_t, out_t, tin, tout, m, n, k, b_col, seed, dist_a, scale_a, dist_b, scale_b, alpha, beta,
+               rows=None, c_scale=1.0):
+    a = torch.empty(m, k, dtype=tin, device=DEV)
+    b = torch.empty((n, k) if b_col else (k, n), dtype=tin, device=DEV)
+    gz.fill(a, seed, 1, dist_a, scale_a)
+    gz.fill(b, seed, 2, dist_b, scale_b)
+    c = None
+    if beta != 0:
+        c = torch.empty(m, n, dtype=tout, device=DEV)
+        gz.fill(c, seed, 3, 1, c_scale)
+    d = torch.full((m, n), 7, dtype=tout, device=DEV)
+    g = gz.Sm100Gemm(m, n, k, in_t, out_t, layout_b=gz.COL_MAJOR if b_col else gz.ROW_MAJOR)
+    g(a, b, c, d, alpha, beta)
+    st, detail = g.plan.device_status()
+    assert st == 0, detail
+    ah, bh = orc.bits_of(a), orc.bits_of(b)
+    ch = orc.bits_of(c) if c is not None else None
+    dh = d.cpu()
+    if rows is not None:
+        rows = np.sort(np.random.default_rng(seed).choice(m, size=min(rows, m), replace=False))
+    got = dh if rows is None else dh[torch.from_numpy(rows)]
+    if in_t == gz.DT_S8:
+        ref = orc.gemm_s8(ah, bh, ch, m, n, k, alpha=int(alpha), beta=int(beta), b_col_major=b_col, rows=rows)
+        assert np.array_equal(got.numpy(), ref)
+        return g.info()
+    ref = orc.gemm_f64(in_t, out_t, ah, bh, ch, m, n, k, alpha=alpha, beta=beta, b_col_major=b_col, rows=rows)
+    scale = orc.abs_gemm(in_t, ah, bh, m, n, k, b_col_major=b_col, rows=rows) * abs(alpha)
+    if c is not None:
+        cc = c.double().cpu().numpy()
+        scale += abs(beta) * np.abs(cc if rows is None else cc[rows])
+    err = np.abs(got.double().numpy() - ref)
+    assert np.isfinite(got.double().numpy()).all()
+    rel_to_max = err.max() / np.abs(ref).max()
+    if in_t == gz.DT_F32:
+        assert (err <= 2.0 ** -9 * scale + 1e-30).all(), (err / scale).max()
+    else:
+        assert rel_to_max <= 1e-2, rel_to_max
+        unit = 2.0 ** -8 if out_t == gz.DT_BF16 else 2.0 ** -10
+        assert (err <= unit * np.abs(ref) + 2.0 ** -20 * scale + 1e-7).all()
+    return g.info()
+
+
+def test_config1_fp16_1024():
+    run_config(gz.DT_F16, gz.DT_F16, torch.float16, torch.float16, 1024, 1024, 1024, True, 0, 0, 1.0, 0, 1.0, 1.0, 0.0)
+
+
+def test_config2_bf16_4096_beta_half():
+    run_config(gz.DT_BF16, gz.DT_BF16, torch.bfloat16, torch.bfloat16, 4096, 4096, 4096, True, 1, 1, 1.0 / 64,
+               1, 1.0 / 64 * 64 ** 0.0, 1.0, 0.5)
+
+
+def test_config3_tf32_8192_row_row():
+    run_config(gz.DT_F32, gz.DT_F32, torch.float32, torch.float32, 8192, 8192, 8192, False, 2, 0, 1.0, 0, 1.0, 1.0, 0.0,
+               rows=64)
+
+
+def test_config4_s8_8192_bit_exact():
+    run_config(gz.DT_S8, gz.DT_S32, torch.int8, torch.int32, 8192, 8192, 8192, True, 3, 2, 1.0, 2, 1.0, 1, 0, rows=64)
+
+
+@pytest.mark.parametrize("m", [1, 16, 128, 2048, 16384])
+def test_config5_inference_sweep(m):
+    run_config(gz.DT_BF16, gz.DT_BF16, torch.bfloat16, torch.bfloat16, m, 14336, 4096, True, 4, 1, 1.0, 1, 0.02, 1.0, 0.0,
+               rows=(None if m <= 2048 else 64))
+
+
+def test_bf16_8192_headline_workload():
+    run_config(gz.DT_BF16, gz.DT_BF16, torch.bfloat16, torch.bfloat16, 8192, 8192, 8192, True, 6, 1, 1.0, 1,
+               8192 ** -0.5, 1.0, 0.0, rows=64)
