@@ -13,7 +13,9 @@ PKG = Path(__file__).resolve().parent
 DT_F16, DT_BF16, DT_F32, DT_S8, DT_S32 = 0, 1, 2, 3, 4
 ROW_MAJOR, COL_MAJOR = 0, 1
 CFG_AUTO, CFG_1CTA_N256, CFG_1CTA_N128, CFG_1CTA_N64, CFG_2CTA_N256, CFG_2CTA_N128, CFG_SIMT = 0, 1, 2, 3, 4, 5, 15
+CFG_SWAP_M16, CFG_SWAP_M32, CFG_SWAP_M64, CFG_SWAP_M128 = 6, 7, 8, 9
 FLAG_EPILOGUE_DIRECT, FLAG_EPILOGUE_TMA, FLAG_TEST_WITHHOLD_ACC_READY = 0x1, 0x2, 0x80000000
+FLAG_NO_SPLIT_K, FLAG_SPLIT_K = 0x4, 0x8
 
 GZ_OK = 0
 GZ_ERR_INVALID_ARG, GZ_ERR_UNSUPPORTED, GZ_ERR_MISALIGNED, GZ_ERR_CUDA = 1, 2, 3, 4
@@ -57,7 +59,8 @@ class PlanInfo(C.Structure):
         ("config", C.c_int32), ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32),
         ("stages", C.c_int32), ("ctas_per_tile", C.c_int32), ("grid", C.c_int32),
         ("smem_bytes", C.c_int32), ("epilogue_tma", C.c_int32), ("sm_count", C.c_int32),
-        ("tiles", C.c_int64),
+        ("split_k", C.c_int32), ("reserved", C.c_int32),
+        ("tiles", C.c_int64), ("workspace_bytes", C.c_int64),
         ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64), ("ldd", C.c_int64),
     ]
 

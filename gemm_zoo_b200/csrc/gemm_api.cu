@@ -75,12 +75,14 @@ bool pair_supported(int in, int out) {
 
 struct CfgShape {
   int config, ctas, bn, stages;
-  double eff;  // rough relative efficiency of the tile shape, for the chooser only
+  bool swap;  // operand roles exchanged: the 128-row side walks N, the bn side walks M
 };
 const CfgShape kShapes[] = {
-    {GZ_CFG_2CTA_N256, 2, 256, 6, 1.00}, {GZ_CFG_1CTA_N256, 1, 256, 4, 0.90},
-    {GZ_CFG_2CTA_N128, 2, 128, 8, 0.80}, {GZ_CFG_1CTA_N128, 1, 128, 6, 0.72},
-    {GZ_CFG_1CTA_N64, 1, 64, 8, 0.45},
+    {GZ_CFG_2CTA_N256, 2, 256, 6, false}, {GZ_CFG_1CTA_N256, 1, 256, 4, false},
+    {GZ_CFG_2CTA_N128, 2, 128, 8, false}, {GZ_CFG_1CTA_N128, 1, 128, 6, false},
+    {GZ_CFG_1CTA_N64, 1, 64, 8, false},   {GZ_CFG_SWAP_M16, 1, 16, 12, true},
+    {GZ_CFG_SWAP_M32, 1, 32, 11, true},   {GZ_CFG_SWAP_M64, 1, 64, 9, true},
+    {GZ_CFG_SWAP_M128, 1, 128, 6, true},
 };
 const CfgShape* shape_of(int config) {
   for (const auto& s : kShapes)
@@ -109,7 +111,9 @@ gz_status normalise(const gz_gemm_desc* desc, Problem* pr) {
   if (d.device < 0) return GZ_ERR_INVALID_ARG;
   if ((d.flags & GZ_FLAG_EPILOGUE_DIRECT) && (d.flags & GZ_FLAG_EPILOGUE_TMA))
     return GZ_ERR_INVALID_ARG;
-  if (d.flags & ~(GZ_FLAG_EPILOGUE_DIRECT | GZ_FLAG_EPILOGUE_TMA | 0x80000000u))
+  if ((d.flags & GZ_FLAG_NO_SPLIT_K) && (d.flags & GZ_FLAG_SPLIT_K)) return GZ_ERR_INVALID_ARG;
+  if (d.flags & ~(GZ_FLAG_EPILOGUE_DIRECT | GZ_FLAG_EPILOGUE_TMA | GZ_FLAG_NO_SPLIT_K | GZ_FLAG_SPLIT_K |
+                  GZ_FLAG_TEST_WITHHOLD_ACC_READY))
     return GZ_ERR_INVALID_ARG;
   if (!pair_supported(d.in_type, d.out_type)) return GZ_ERR_UNSUPPORTED;
   if (d.config != GZ_CFG_AUTO && d.config != GZ_CFG_SIMT && !shape_of(d.config))
@@ -141,24 +145,52 @@ gz_status normalise(const gz_gemm_desc* desc, Problem* pr) {
 // edge (in elements) must hold at least one chunk: 128 for s8, 64 for 16-bit, 32 for fp32.
 bool shape_fits(const Problem& pr, const CfgShape& s) {
   const int chunk = 128 / pr.in_size;
-  if (pr.b_mn_major && (s.bn / s.ctas) % chunk != 0) return false;
-  if (pr.a_mn_major && 128 % chunk != 0) return false;
+  // Which matrix rides the 128-row side and which the bn side of the MMA.
+  const bool wide_mn_major = s.swap ? pr.b_mn_major : pr.a_mn_major;
+  const bool narrow_mn_major = s.swap ? pr.a_mn_major : pr.b_mn_major;
+  if (narrow_mn_major && (s.bn / s.ctas) % chunk != 0) return false;
+  if (wide_mn_major && 128 % chunk != 0) return false;
+  if (s.swap && pr.d.m > s.bn) return false;  // swapped tiles cover all of M with one tile
   return true;
 }
 
-// Pick the tile shape with the least estimated time: waves of tiles over the
-// SMs, each wave costing the per-SM tile area divided by the shape's efficiency.
+// Split-K is implemented by the swapped (skinny) tiles only.  It pays when whole tiles would
+// occupy at most half of the SMs (with more than that streaming, HBM is already saturated) and
+// every CTA still gets a few K blocks.
+bool wants_split_k(const Problem& pr, const CfgShape& s, int sm_count) {
+  if (!s.swap || (pr.d.flags & GZ_FLAG_NO_SPLIT_K)) return false;
+  const int64_t k_blocks = cdiv(pr.d.k, 128 / pr.in_size);
+  const int64_t tiles = cdiv(pr.d.n, 128) * cdiv(pr.d.m, s.bn);
+  const int64_t total = tiles * k_blocks;
+  if (total < 2) return false;
+  if (pr.d.flags & GZ_FLAG_SPLIT_K) return true;
+  return tiles * 2 <= sm_count && total >= (int64_t)sm_count * 4;
+}
+
+// Pick the tile shape with the least estimated time.  Per 128-byte K block a CTA is held up by
+// the slowest of: the MMAs (a 128 x bn x 32-byte MMA takes bn/2 cycles, four per block), the
+// L2 -> shared-memory fill of its stage (about 64 bytes per cycle per SM), and the issue cost of
+// the block (about 250 cycles).  Whole tiles are dealt to the SMs in waves; with split-K the K
+// blocks of all tiles are spread evenly.
 int choose_config(const Problem& pr, int sm_count) {
   if (!pr.tma_ld_ok) return GZ_CFG_SIMT;
   double best = 0;
-  int best_cfg = GZ_CFG_1CTA_N128;
+  int best_cfg = GZ_CFG_SIMT;
+  const int64_t k_blocks = cdiv(pr.d.k, 128 / pr.in_size);
   for (const auto& s : kShapes) {
     if (!shape_fits(pr, s)) continue;
-    const int64_t tiles = cdiv(pr.d.m, 128 * s.ctas) * cdiv(pr.d.n, s.bn);
+    const int64_t wide = s.swap ? pr.d.n : pr.d.m, narrow = s.swap ? pr.d.m : pr.d.n;
+    const int64_t tiles = cdiv(wide, 128 * s.ctas) * cdiv(narrow, s.bn);
     const int64_t units = sm_count / s.ctas;
     if (units <= 0) continue;
-    const int64_t waves = cdiv(tiles, units);
-    const double cost = double(waves) * (128.0 * s.bn) / s.eff;
+    const double mma = 4.0 * (s.bn / 2.0);
+    const double fill = (128.0 + double(s.bn) / s.ctas) * 128.0 / 64.0;
+    const double issue = 250.0;
+    double per_block = mma > fill ? mma : fill;
+    if (issue > per_block) per_block = issue;
+    const int64_t blocks_per_cta =
+        wants_split_k(pr, s, sm_count) ? cdiv(tiles * k_blocks, units) : cdiv(tiles, units) * k_blocks;
+    const double cost = double(blocks_per_cta) * per_block;
     if (best == 0 || cost < best) {
       best = cost;
       best_cfg = s.config;
@@ -187,17 +219,25 @@ void fill_info(const Problem& pr, int config, int sm_count, gz_plan_info* info) 
     return;
   }
   const CfgShape* s = shape_of(config);
-  info->tile_m = 128 * s->ctas;
-  info->tile_n = s->bn;
+  info->tile_m = s->swap ? s->bn : 128 * s->ctas;
+  info->tile_n = s->swap ? 128 : s->bn;
   info->tile_k = 128 / pr.in_size;
   info->stages = s->stages;
   info->ctas_per_tile = s->ctas;
-  info->tiles = cdiv(pr.d.m, info->tile_m) * cdiv(pr.d.n, s->bn);
+  info->tiles = cdiv(pr.d.m, info->tile_m) * cdiv(pr.d.n, info->tile_n);
   const int64_t units = sm_count / s->ctas;
   info->grid = (int32_t)((info->tiles < units ? info->tiles : units) * s->ctas);
-  info->smem_bytes = 1024 + s->stages * (128 * 128 + (s->bn / s->ctas) * 128) + 4 * 2 * 4096 + 256;
-  const bool d_tma_ok = (pr.d.ldd * pr.out_size) % 16 == 0;
-  info->epilogue_tma = (pr.d.flags & GZ_FLAG_EPILOGUE_DIRECT) ? 0 : (d_tma_ok ? 1 : 0);
+  if (wants_split_k(pr, *s, sm_count)) {
+    const int64_t k_blocks = cdiv(pr.d.k, info->tile_k);
+    const int64_t total = info->tiles * k_blocks;
+    const int64_t grid = units < total ? units : total;
+    const int64_t shortest = total / grid;  // K blocks in the shortest range
+    const int64_t contrib = (k_blocks - 1) / shortest + 2;
+    info->split_k = 1;
+    info->grid = (int32_t)grid;
+    info->workspace_bytes = info->tiles * contrib * (int64_t)s->bn * 128 * 4 + info->tiles * 4;
+    info->reserved = (int32_t)contrib;
+  }
 }
 
 using LaunchFn = cudaError_t (*)(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
@@ -220,12 +260,14 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = Cfg::CTAS;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  if (Cfg::CTAS > 1) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = Cfg::CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
   return cudaLaunchKernelEx(&cfg, gz::sm100_gemm_kernel<Cfg, PROF>, ta, tb, td, p);
 }
 
@@ -265,6 +307,22 @@ KernelEntry entry_for_shape(int config) {
     case GZ_CFG_1CTA_N64: {
       using C = gz::GemmCfg<KIND, TOut, 64, 1, 8>;
       return make_entry<C, WITH_PROF>();
+    }
+    case GZ_CFG_SWAP_M16: {
+      using C = gz::GemmCfg<KIND, TOut, 16, 1, 12, true>;
+      return make_entry<C, WITH_PROF>();
+    }
+    case GZ_CFG_SWAP_M32: {
+      using C = gz::GemmCfg<KIND, TOut, 32, 1, 11, true>;
+      return make_entry<C, WITH_PROF>();
+    }
+    case GZ_CFG_SWAP_M64: {
+      using C = gz::GemmCfg<KIND, TOut, 64, 1, 9, true>;
+      return make_entry<C, WITH_PROF>();
+    }
+    case GZ_CFG_SWAP_M128: {
+      using C = gz::GemmCfg<KIND, TOut, 128, 1, 6, true>;
+      return make_entry<C, false>();
     }
   }
   return {nullptr, nullptr, nullptr, nullptr};
@@ -345,6 +403,7 @@ struct gz_plan {
   KernelEntry entry;
   gz::GemmParams base;  // everything that does not depend on the operand pointers
   uint32_t* status_dev;
+  void* workspace;  // split-K partial sums followed by the per-tile arrival counters
   // device staging for gz_gemm_run_host
   void *ha, *hb, *hc, *hd;
   size_t ha_bytes, hb_bytes, hcd_bytes;
@@ -397,8 +456,8 @@ uint32_t build_idesc(const Problem& pr, const CfgShape& s) {
   idesc |= fmt_c << 4;
   idesc |= fmt_ab << 7;
   idesc |= fmt_ab << 10;
-  idesc |= (pr.a_mn_major ? 1u : 0u) << 15;
-  idesc |= (pr.b_mn_major ? 1u : 0u) << 16;
+  idesc |= ((s.swap ? pr.b_mn_major : pr.a_mn_major) ? 1u : 0u) << 15;
+  idesc |= ((s.swap ? pr.a_mn_major : pr.b_mn_major) ? 1u : 0u) << 16;
   idesc |= (uint32_t)(s.bn >> 3) << 17;
   idesc |= (uint32_t)((128 * s.ctas) >> 4) << 24;
   return idesc;
@@ -512,6 +571,7 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
   if (!pl) return GZ_ERR_OUT_OF_MEMORY;
   pl->pr = pr;
   pl->status_dev = nullptr;
+  pl->workspace = nullptr;
   pl->ha = pl->hb = pl->hc = pl->hd = nullptr;
   pl->ha_bytes = pl->hb_bytes = pl->hcd_bytes = 0;
   fill_info(pr, config, sm_count, &pl->info);
@@ -539,17 +599,19 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
       return GZ_ERR_CUDA;
     }
     gz::GemmParams& p = pl->base;
-    build_operand(&p.a, pr.a_mn_major, 128, pr.in_size);
-    build_operand(&p.b, pr.b_mn_major, s.bn / s.ctas, pr.in_size);
+    // Operand "a" of the kernel is whatever rides the 128-row side of the MMA.
+    build_operand(&p.a, s.swap ? pr.b_mn_major : pr.a_mn_major, 128, pr.in_size);
+    build_operand(&p.b, s.swap ? pr.a_mn_major : pr.b_mn_major, s.bn / s.ctas, pr.in_size);
     const uint32_t tile_m = 128u * s.ctas;
-    p.grid.tiles_m = (uint32_t)cdiv(pr.d.m, tile_m);
-    p.grid.tiles_n = (uint32_t)cdiv(pr.d.n, s.bn);
+    const int64_t wide = s.swap ? pr.d.n : pr.d.m, narrow = s.swap ? pr.d.m : pr.d.n;
+    p.grid.tiles_m = (uint32_t)cdiv(wide, tile_m);
+    p.grid.tiles_n = (uint32_t)cdiv(narrow, s.bn);
     // Rows of tiles that run concurrently should span about as many output rows as columns.
     uint32_t gm = 2048u / tile_m;
     p.grid.group_m = gm < 1 ? 1 : gm;
     p.grid.num_tiles = p.grid.tiles_m * p.grid.tiles_n;
-    p.m = (uint32_t)pr.d.m;
-    p.n = (uint32_t)pr.d.n;
+    p.m = (uint32_t)wide;
+    p.n = (uint32_t)narrow;
     p.k = (uint32_t)pr.d.k;
     p.bk = 128u / pr.in_size;
     p.k_blocks = (uint32_t)cdiv(pr.d.k, p.bk);
@@ -566,6 +628,22 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
     p.ldd = pr.d.ldd;
     p.status = pl->status_dev;
     p.wait_limit_ns = pr.d.wait_limit_ns;
+    if (pl->info.split_k) {
+      const size_t ws_bytes = (size_t)pl->info.workspace_bytes;
+      const size_t counter_bytes = (size_t)p.grid.num_tiles * 4;
+      if (!cuda_ok(cudaMalloc(&pl->workspace, ws_bytes), "cudaMalloc(split-K workspace)") ||
+          !cuda_ok(cudaMemset(pl->workspace, 0, ws_bytes), "cudaMemset(split-K workspace)")) {
+        if (pl->workspace) cudaFree(pl->workspace);
+        cudaFree(pl->status_dev);
+        delete pl;
+        return GZ_ERR_OUT_OF_MEMORY;
+      }
+      p.split_k = 1;
+      p.max_contrib = (uint32_t)pl->info.reserved;
+      p.total_kb = (unsigned long long)p.grid.num_tiles * p.k_blocks;
+      p.ws = static_cast<float*>(pl->workspace);
+      p.counters = reinterpret_cast<int*>(static_cast<char*>(pl->workspace) + (ws_bytes - counter_bytes));
+    }
   }
   *out = pl;
   return GZ_OK;
@@ -575,6 +653,7 @@ GZ_API gz_status gz_gemm_plan_destroy(gz_plan* pl) {
   if (!pl) return GZ_ERR_INVALID_ARG;
   (void)cudaSetDevice(pl->pr.d.device);
   if (pl->status_dev) cudaFree(pl->status_dev);
+  if (pl->workspace) cudaFree(pl->workspace);
   if (pl->ha) cudaFree(pl->ha);
   if (pl->hb) cudaFree(pl->hb);
   if (pl->hc) cudaFree(pl->hc);
@@ -661,20 +740,23 @@ GZ_API gz_status gz_gemm_run(gz_plan* pl, const void* a, const void* b, const vo
 
   CUtensorMap ta, tb, td;
   const uint32_t bk = 128u / pr.in_size;
+  // Tensor map of one input matrix: `rows` is its M (or N) extent, `od` the kernel operand it feeds.
+  auto encode_input = [&](CUtensorMap* tm, const void* base, bool mn_major, int64_t rows, int64_t ld,
+                          const gz::OperandDesc& od) {
+    if (!mn_major)
+      return encode_2d(tm, pr.d.in_type, base, (uint64_t)pr.d.k, (uint64_t)rows, (uint64_t)ld * pr.in_size,
+                       bk, od.box_mn, true);
+    return encode_2d(tm, pr.d.in_type, base, (uint64_t)rows, (uint64_t)pr.d.k, (uint64_t)ld * pr.in_size,
+                     od.box_mn, bk, true, pr.in_size == 4);
+  };
   bool ok;
-  if (!pr.a_mn_major)
-    ok = encode_2d(&ta, pr.d.in_type, a, (uint64_t)pr.d.k, (uint64_t)pr.d.m,
-                   (uint64_t)pr.d.lda * pr.in_size, bk, 128, true);
-  else
-    ok = encode_2d(&ta, pr.d.in_type, a, (uint64_t)pr.d.m, (uint64_t)pr.d.k,
-                   (uint64_t)pr.d.lda * pr.in_size, p.a.box_mn, bk, true, pr.in_size == 4);
-  if (!ok) return GZ_ERR_CUDA;
-  if (!pr.b_mn_major)
-    ok = encode_2d(&tb, pr.d.in_type, b, (uint64_t)pr.d.k, (uint64_t)pr.d.n,
-                   (uint64_t)pr.d.ldb * pr.in_size, bk, (uint32_t)(s.bn / s.ctas), true);
-  else
-    ok = encode_2d(&tb, pr.d.in_type, b, (uint64_t)pr.d.n, (uint64_t)pr.d.k,
-                   (uint64_t)pr.d.ldb * pr.in_size, p.b.box_mn, bk, true, pr.in_size == 4);
+  if (!s.swap) {
+    ok = encode_input(&ta, a, pr.a_mn_major, pr.d.m, pr.d.lda, p.a) &&
+         encode_input(&tb, b, pr.b_mn_major, pr.d.n, pr.d.ldb, p.b);
+  } else {
+    ok = encode_input(&ta, b, pr.b_mn_major, pr.d.n, pr.d.ldb, p.a) &&
+         encode_input(&tb, a, pr.a_mn_major, pr.d.m, pr.d.lda, p.b);
+  }
   if (!ok) return GZ_ERR_CUDA;
   if (p.epilogue_tma) {
     ok = encode_2d(&td, pr.d.out_type, d, (uint64_t)pr.d.n, (uint64_t)pr.d.m,

@@ -38,6 +38,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "ptx.cuh"
 #include "tile_sched.h"
 
@@ -81,6 +83,14 @@ struct GemmParams {
   void* d;
   uint32_t* status;  // 4 words in global memory
   uint64_t wait_limit_ns;
+  // Split-K work distribution (0 = whole tiles, dealt round-robin).  When set, the K blocks of all
+  // tiles form one line that is cut into equal contiguous ranges, one per CTA; a tile whose K range
+  // is shared by several CTAs is finished by whichever of them arrives last (see the epilogue).
+  uint32_t split_k;
+  uint32_t max_contrib;          // workspace slots per tile
+  unsigned long long total_kb;   // num_tiles * k_blocks
+  float* ws;                     // [num_tiles][max_contrib][128][BN] partial accumulators (fp32 or int32 bits)
+  int* counters;                 // [num_tiles], zero between launches
   // Tuning switches (see TUNE_* below).
   uint32_t tune;
   // Optional stall counters, 16 words per CTA (null = off):
@@ -90,6 +100,7 @@ struct GemmParams {
   //  [6] epilogue warp 2: total clocks                 [7] MMA: elapsed nanoseconds (globaltimer)
   //  [8] A producer: clocks issuing copies               [9] MMA: clocks issuing MMAs and commits
   //  [10] B producer: clocks waiting for a free stage   [11] B producer: clocks issuing copies
+  //  [12] epilogue warp 2: clocks parking split-K partial sums
   // Only kernels instantiated with PROF = true write them.
   unsigned long long* prof;
 };
@@ -99,9 +110,15 @@ enum : uint32_t {
   TUNE_L2_PREFETCH_SHIFT = 8,  // bits 8..15: prefetch operand tiles into L2 this many K blocks ahead
 };
 
-template <ptx::Kind KIND_, typename TOut_, int BN_, int CTAS_, int STAGES_>
+// SWAP_: the roles of the operands are exchanged.  The 128-row side of the MMA (TMEM lanes) walks N
+// and carries B; the narrow side (BN = 16..128 TMEM columns) carries the few rows of A.  Used for
+// skinny problems (M <= 128), where a 128-row A tile would be mostly padding: every byte a stage
+// loads is then a useful byte of B, which is what such HBM-bound shapes need.  The accumulator
+// holds the transpose of the output tile; the epilogue stores it straight to global memory.
+template <ptx::Kind KIND_, typename TOut_, int BN_, int CTAS_, int STAGES_, bool SWAP_ = false>
 struct GemmCfg {
   static constexpr ptx::Kind KIND = KIND_;
+  static constexpr bool SWAP = SWAP_;
   using TOut = TOut_;
   static constexpr int BN = BN_;        // tile columns (= MMA N)
   static constexpr int CTAS = CTAS_;    // CTAs sharing one tile (1 or 2)
@@ -111,16 +128,17 @@ struct GemmCfg {
   static constexpr int A_BYTES = BM * 128;       // one stage of A: 128 rows x 128 bytes
   static constexpr int B_BYTES = BN_CTA * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGING_WARP_BYTES = 2 * 4096;  // two 32-row x 128-byte boxes per warp
+  static constexpr int STAGING_WARP_BYTES = SWAP ? 0 : 2 * 4096;  // two 32-row x 128-byte boxes per warp
   static constexpr int STAGING_BYTES = 4 * STAGING_WARP_BYTES;
   static constexpr int BAR_BYTES = 256;
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators
   static constexpr int THREADS = 224;  // 2 producer warps, 1 MMA warp, 4 epilogue warps
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
-  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile N");
-  static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "tile N");
+  static_assert(!SWAP || (CTAS == 1 && BN <= 128), "swapped tiles are single-CTA and narrow");
+  static_assert(TMEM_COLS == 32 || TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
                 "TMEM allocation must be a power of two");
-  static_assert(8 * (2 * STAGES + 5) + 8 <= BAR_BYTES, "barrier area");
+  static_assert(8 * (2 * STAGES + 5) + 12 <= BAR_BYTES, "barrier area");
   static_assert(STAGE_BYTES % 1024 == 0, "stage must keep 1024-byte alignment");
 };
 
@@ -175,6 +193,45 @@ __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, const Abort&
       }
     }
   }
+}
+
+// The sequence of (tile, K-block range) pieces one CTA (or CTA pair) works through.  Every role
+// of the CTA constructs the same iterator and so sees the same sequence.
+struct WorkIter {
+  uint32_t k_blocks, num_tiles, step, next_tile;
+  unsigned long long cur, end;
+  bool split;
+  __device__ __forceinline__ WorkIter(const GemmParams& p, uint32_t cluster, uint32_t num_clusters)
+      : k_blocks(p.k_blocks), num_tiles(p.grid.num_tiles), step(num_clusters), next_tile(cluster),
+        cur(0), end(0), split(p.split_k != 0u) {
+    if (split) {
+      cur = static_cast<unsigned long long>(cluster) * p.total_kb / num_clusters;
+      end = static_cast<unsigned long long>(cluster + 1u) * p.total_kb / num_clusters;
+    }
+  }
+  __device__ __forceinline__ bool next(uint32_t& tile, uint32_t& kb_lo, uint32_t& kb_hi) {
+    if (!split) {
+      if (next_tile >= num_tiles) return false;
+      tile = next_tile;
+      kb_lo = 0;
+      kb_hi = k_blocks;
+      next_tile += step;
+      return true;
+    }
+    if (cur >= end) return false;
+    tile = static_cast<uint32_t>(cur / k_blocks);
+    kb_lo = static_cast<uint32_t>(cur - static_cast<unsigned long long>(tile) * k_blocks);
+    const unsigned long long left = end - cur;
+    kb_hi = (left < k_blocks - kb_lo) ? kb_lo + static_cast<uint32_t>(left) : k_blocks;
+    cur += kb_hi - kb_lo;
+    return true;
+  }
+};
+
+// Index of the CTA whose contiguous range contains K-block unit `u` (inverse of the cut above).
+__device__ __forceinline__ uint32_t split_owner(unsigned long long u, unsigned long long total,
+                                                uint32_t parts) {
+  return static_cast<uint32_t>(((u + 1ull) * parts + total - 1ull) / total - 1ull);
 }
 
 template <typename TOut>
@@ -280,6 +337,23 @@ __device__ __forceinline__ void epilogue_math(uint32_t (&v)[32], const GemmParam
   }
 }
 
+// alpha * acc (+ beta * *c) for a single element (the swapped-operand epilogue).
+template <typename TOut, bool HAS_BETA>
+__device__ __forceinline__ TOut epilogue_scalar(uint32_t acc, const GemmParams& p, const TOut* c) {
+  using Tr = OutTraits<TOut>;
+  if constexpr (Tr::INT) {
+    uint32_t v = static_cast<uint32_t>(p.alpha_i) * acc;
+    if constexpr (HAS_BETA) v += static_cast<uint32_t>(p.beta_i) * static_cast<uint32_t>(*c);
+    return static_cast<int32_t>(v);
+  } else {
+    float f = p.alpha_f * __uint_as_float(acc);
+    if constexpr (HAS_BETA) f = fmaf(p.beta_f, Tr::to_f(*c), f);
+    if constexpr (sizeof(TOut) == 4) return f;
+    else if constexpr (std::is_same<TOut, __half>::value) return __float2half_rn(f);
+    else return __float2bfloat16_rn(f);
+  }
+}
+
 // Store one packed 32-column slice of one row straight to global memory.
 template <typename TOut>
 __device__ __forceinline__ void store_direct(const uint32_t (&v)[32], TOut* drow, uint32_t ncols,
@@ -332,6 +406,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const uint32_t drain_bar = bars + 8u * (2 * STAGES + 4);
   uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars_ptr + 8 * (2 * STAGES + 5));
   uint32_t* const abort_flag = tmem_slot + 1;
+  uint32_t* const split_flag = tmem_slot + 2;  // epilogue: "this CTA finishes the tile"
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
@@ -342,22 +417,25 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const detail::Abort ab{abort_flag, p.status, p.wait_limit_ns};
 
   // ------------------------------------------------------------ set-up
-  if (threadIdx.x == 0) {
-    *abort_flag = 0u;
-    for (uint32_t s = 0; s < STAGES; ++s) {
+  if (warp == 0) {
+    for (uint32_t s = lane; s < STAGES; s += 32u) {
       ptx::mbar_init(full_bar(s), 2);  // one arrive.expect_tx per producer warp
       ptx::mbar_init(empty_bar(s), 1);
     }
-    for (uint32_t b = 0; b < 2; ++b) {
-      ptx::mbar_init(tmem_full_bar(b), 1);
-      ptx::mbar_init(tmem_empty_bar(b), 128 * CTAS);
+    if (lane < 2u) {
+      ptx::mbar_init(tmem_full_bar(lane), 1);
+      ptx::mbar_init(tmem_empty_bar(lane), 128 * CTAS);
     }
-    ptx::mbar_init(drain_bar, 1);
+    if (lane == 2u) {
+      ptx::mbar_init(drain_bar, 1);
+      *abort_flag = 0u;
+      *split_flag = 0u;
+    }
     ptx::fence_mbar_init_cluster();
-    ptx::prefetch_tensormap(&tm_a);
-    ptx::prefetch_tensormap(&tm_b);
-    if (p.epilogue_tma) ptx::prefetch_tensormap(&tm_d);
+    if (lane == 3u) ptx::prefetch_tensormap(&tm_a);
+    if (lane == 4u && p.epilogue_tma) ptx::prefetch_tensormap(&tm_d);
   }
+  if (warp == 6 && lane == 0) ptx::prefetch_tensormap(&tm_b);
   if (warp == 1) {
     ptx::tmem_alloc<CTAS>(ptx::smem_u32(tmem_slot), Cfg::TMEM_COLS);
     ptx::tmem_relinquish<CTAS>();
@@ -393,12 +471,14 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     bool ok = true;
     long long prof_wait = 0, prof_issue = 0;
     const long long prof_t0 = PROF ? clock64() : 0;
-    for (uint32_t t = cluster; ok && t < num_tiles; t += num_clusters) {
+    detail::WorkIter work(p, cluster, num_clusters);
+    uint32_t t = 0, kb_lo = 0, kb_hi = 0;
+    while (ok && work.next(t, kb_lo, kb_hi)) {
       uint32_t tm, tn;
       tile_coords(p.grid, t, tm, tn);
       const int32_t row0 = is_b ? static_cast<int32_t>(tn * BN + rank * Cfg::BN_CTA)
                                 : static_cast<int32_t>(tm * (128u * CTAS) + rank * 128u);
-      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+      for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
         const long long w0 = PROF ? clock64() : 0;
         const bool got = detail::wait(empty_bar(stage), phase ^ 1u, ab, WAIT_PRODUCER_EMPTY, t, kb);
         ok = __all_sync(0xFFFFFFFFu, got);
@@ -424,7 +504,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             else
               ptx::tma_load_2d_pair(dst + i * box_bytes, tmap, mn_major ? mn : k0, mn_major ? k0 : mn, fb);
           }
-          if (l2_dist != 0u && kb + l2_dist < k_blocks) {
+          if (l2_dist != 0u && kb + l2_dist < kb_hi) {
             const int32_t kp = static_cast<int32_t>((kb + l2_dist) * bk);
             for (uint32_t i = 0; i < boxes; ++i) {
               const int32_t mn = row0 + static_cast<int32_t>(i * box_mn);
@@ -477,7 +557,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint32_t b_lo0 = (((base + Cfg::A_BYTES) >> 4) & 0x3FFFu) | p.b.desc_lo;
       const uint32_t a_step = p.a.k_step16, b_step = p.b.k_step16;
       const uint32_t idesc = p.idesc;
-      for (uint32_t t = cluster; ok && t < num_tiles; t += num_clusters) {
+      detail::WorkIter work(p, cluster, num_clusters);
+      uint32_t t = 0, kb_lo = 0, kb_hi = 0;
+      while (ok && work.next(t, kb_lo, kb_hi)) {
         const long long w0 = PROF ? clock64() : 0;
         const bool got0 = detail::wait<CTAS == 2>(tmem_empty_bar(acc), acc_phase ^ 1u, ab,
                                                   WAIT_MMA_TMEM_EMPTY, t, 0);
@@ -486,7 +568,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if constexpr (PROF) prof_tmem += clock64() - w0;
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
           const long long w1 = PROF ? clock64() : 0;
           const bool got = detail::wait(full_bar(stage), phase, ab, WAIT_MMA_FULL, t, kb);
           ok = __all_sync(0xFFFFFFFFu, got);
@@ -501,7 +583,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             for (uint32_t j = 0; j < 4; ++j) {  // 128 bytes of K per stage, 32 bytes per MMA
               const uint64_t ad = (static_cast<uint64_t>(a_hi) << 32) | (a_lo + j * a_step);
               const uint64_t bd = (static_cast<uint64_t>(b_hi) << 32) | (b_lo + j * b_step);
-              ptx::umma<Cfg::KIND, CTAS>(d_tmem, ad, bd, idesc, (kb | j) != 0u ? 1u : 0u);
+              ptx::umma<Cfg::KIND, CTAS>(d_tmem, ad, bd, idesc, (kb != kb_lo || j != 0u) ? 1u : 0u);
             }
             // Release the stage to the producer(s) once these MMAs have read it.
             if constexpr (CTAS == 2) {
@@ -569,13 +651,15 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     uint32_t acc = 0, acc_phase = 0, sbuf = 0;
     bool ok = true;
     const bool prof = PROF && p.prof != nullptr && warp == 2 && lane == 0;
-    long long prof_wait = 0;
+    long long prof_wait = 0, prof_park = 0;
     const long long prof_t0 = prof ? clock64() : 0;
     const TOut* const cmat = static_cast<const TOut*>(p.c);
     TOut* const dmat = static_cast<TOut*>(p.d);
     const uint32_t tmem_empty_target =
         (CTAS == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
-    for (uint32_t t = cluster; ok && t < num_tiles; t += num_clusters) {
+    detail::WorkIter work(p, cluster, num_clusters);
+    uint32_t t = 0, kb_lo = 0, kb_hi = 0;
+    while (ok && work.next(t, kb_lo, kb_hi)) {
       uint32_t tm, tn;
       tile_coords(p.grid, t, tm, tn);
       const long long w0 = prof ? clock64() : 0;
@@ -585,56 +669,173 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
       if (prof) prof_wait += clock64() - w0;
       ptx::tc_fence_after_sync();
-      const uint32_t row0 = tm * (128u * CTAS) + rank * 128u + quad * 32u;  // first row of this warp
-      const uint32_t row = row0 + lane;
-      const bool row_ok = row < p.m;
-      const uint32_t col_tile = tn * BN;
-      const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
-      if (row0 < p.m) {
-        for (uint32_t box = 0; box < BN / BOX_COLS; ++box) {
-          const uint32_t box_col = col_tile + box * BOX_COLS;
-          if (box_col >= p.n) break;
-          const uint32_t sb_addr = stg + sbuf * 4096u;
-          if (p.epilogue_tma) {
-            // The buffer about to be overwritten was handed to a TMA store two boxes ago.
-            if (lane == 0) ptx::bulk_wait_group_read<1>();
-            __syncwarp();
-          }
+      if constexpr (Cfg::SWAP) {
+        // Accumulator lane = output column (n), accumulator column = output row (m).
+        const uint32_t ncol0 = tm * 128u + quad * 32u;  // first n of this warp
+        const uint32_t ncol = ncol0 + lane;
+        const bool n_ok = ncol < p.m;                   // p.m is the extent of the 128-row side (N)
+        const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
+        const bool partial = (kb_lo != 0u) || (kb_hi != k_blocks);
+        uint32_t contributors = 1, my_slot = 0;
+        bool finish = true;  // this CTA writes the tile's output
+        if (partial && detail::aborted(ab)) {  // never enter the CTA-wide barrier below while aborting
+          ok = false;
+          break;
+        }
+        const long long e0 = prof ? clock64() : 0;
+        // Workspace layout: [tile][slot][128 accumulator lanes][BN columns]; a thread owns one
+        // lane's BN consecutive floats and moves them 16 bytes at a time.
+        const size_t lane_off = static_cast<size_t>(quad * 32u + lane) * BN;
+        if (partial) {
+          // This CTA holds only part of the tile's K range.  Park the partial accumulator in this
+          // CTA's workspace slot; the CTA that arrives last adds the slots in K order and writes
+          // the output, so the result does not depend on arrival order.
+          const unsigned long long tile_u0 = static_cast<unsigned long long>(t) * k_blocks;
+          const uint32_t first = detail::split_owner(tile_u0, p.total_kb, num_clusters);
+          const uint32_t last = detail::split_owner(tile_u0 + k_blocks - 1u, p.total_kb, num_clusters);
+          contributors = last - first + 1u;
+          my_slot = cluster - first;
+          float4* slot = reinterpret_cast<float4*>(
+              p.ws + (static_cast<size_t>(t) * p.max_contrib + my_slot) * (BN * 128u) + lane_off);
 #pragma unroll
-          for (int sl = 0; sl < SLICES; ++sl) {
-            const uint32_t col0 = box_col + sl * 32u;
-            if (col0 >= p.n) break;  // uniform across the warp
-            const uint32_t ncols = (p.n - col0 < 32u) ? (p.n - col0) : 32u;
-            uint32_t v[32];
-            ptx::tmem_ld_32x32(taddr + box * BOX_COLS + sl * 32u, v);
+          for (int sl = 0; sl < BN / 16; ++sl) {
+            uint32_t v[16];
+            ptx::tmem_ld_32x16(taddr + sl * 16u, v);
             ptx::tmem_wait_ld();
-            const TOut* crow = cmat + static_cast<int64_t>(row) * p.ldc + col0;
-            detail::epilogue_math<TOut>(v, p, crow, row_ok, ncols);
-            if (p.epilogue_tma) {
-              // Row `lane` of the staged box; 16-byte chunk j lands at j ^ (lane % 8),
-              // the layout a 128B-swizzled tensor map expects.
 #pragma unroll
-              for (int q = 0; q < WORDS / 4; ++q) {
-                const uint32_t j = static_cast<uint32_t>(sl * (WORDS / 4) + q);
-                const uint32_t addr = sb_addr + lane * 128u + ((j ^ (lane & 7u)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v[4 * q]),
-                             "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
-                             : "memory");
+            for (int q = 0; q < 4; ++q)
+              slot[sl * 4 + q] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                             __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+          }
+          __threadfence();
+          ptx::named_barrier_sync(1, 128);  // all four epilogue warps have parked their rows
+          if (warp == 2 && lane == 0) {
+            const int old = atomicAdd(p.counters + t, 1);
+            const bool is_last = static_cast<uint32_t>(old) == contributors - 1u;
+            if (is_last) p.counters[t] = 0;  // leave the counter clean for the next launch
+            *split_flag = is_last ? 1u : 0u;
+          }
+          ptx::named_barrier_sync(1, 128);
+          finish = *reinterpret_cast<volatile uint32_t*>(split_flag) != 0u;
+          if (finish) __threadfence();
+        }
+        const long long e1 = prof ? clock64() : 0;
+        if (prof) prof_park += e1 - e0;
+        if (finish && ncol0 < p.m) {
+          const bool has_beta = detail::OutTraits<TOut>::INT ? (p.beta_i != 0) : (p.beta_f != 0.0f);
+#pragma unroll
+          for (int sl = 0; sl < BN / 16; ++sl) {
+            const uint32_t mrow0 = tn * BN + sl * 16u;
+            if (mrow0 >= p.n) break;  // uniform across the warp
+            uint32_t v[16];
+            if (!partial) {
+              ptx::tmem_ld_32x16(taddr + sl * 16u, v);
+              ptx::tmem_wait_ld();
+            } else {
+              const float4* s0 = reinterpret_cast<const float4*>(
+                  p.ws + static_cast<size_t>(t) * p.max_contrib * (BN * 128u) + lane_off) + sl * 4;
+              float4 sum[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) sum[q] = __ldcg(s0 + q);
+              for (uint32_t c = 1; c < contributors; ++c) {
+                const float4* sc = s0 + static_cast<size_t>(c) * (BN * 128u / 4u);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float4 x = __ldcg(sc + q);
+                  if constexpr (detail::OutTraits<TOut>::INT) {
+                    sum[q].x = __uint_as_float(__float_as_uint(sum[q].x) + __float_as_uint(x.x));
+                    sum[q].y = __uint_as_float(__float_as_uint(sum[q].y) + __float_as_uint(x.y));
+                    sum[q].z = __uint_as_float(__float_as_uint(sum[q].z) + __float_as_uint(x.z));
+                    sum[q].w = __uint_as_float(__float_as_uint(sum[q].w) + __float_as_uint(x.w));
+                  } else {
+                    sum[q].x += x.x;
+                    sum[q].y += x.y;
+                    sum[q].z += x.z;
+                    sum[q].w += x.w;
+                  }
+                }
               }
-            } else if (row_ok) {
-              TOut* drow = dmat + static_cast<int64_t>(row) * p.ldd + col0;
-              detail::store_direct<TOut>(v, drow, ncols, p.d_vec_ok != 0u);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                v[4 * q] = __float_as_uint(sum[q].x);
+                v[4 * q + 1] = __float_as_uint(sum[q].y);
+                v[4 * q + 2] = __float_as_uint(sum[q].z);
+                v[4 * q + 3] = __float_as_uint(sum[q].w);
+              }
+            }
+            if (n_ok) {
+              // Column i of the slice is output row mrow0 + i; for each, the 32 lanes of the warp
+              // write 32 consecutive elements of that row.
+              const uint32_t cnt = (p.n - mrow0 < 16u) ? (p.n - mrow0) : 16u;
+              TOut* dp = dmat + static_cast<int64_t>(mrow0) * p.ldd + ncol;
+              const TOut* cp = cmat + static_cast<int64_t>(mrow0) * p.ldc + ncol;
+              if (has_beta) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  if (static_cast<uint32_t>(i) < cnt)
+                    dp[static_cast<int64_t>(i) * p.ldd] =
+                        detail::epilogue_scalar<TOut, true>(v[i], p, cp + static_cast<int64_t>(i) * p.ldc);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  if (static_cast<uint32_t>(i) < cnt)
+                    dp[static_cast<int64_t>(i) * p.ldd] = detail::epilogue_scalar<TOut, false>(v[i], p, nullptr);
+              }
             }
           }
-          if (p.epilogue_tma) {
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              ptx::tma_store_2d(&tm_d, sb_addr, static_cast<int32_t>(box_col),
-                                static_cast<int32_t>(row0));
-              ptx::bulk_commit_group();
+        }
+      } else {
+        const uint32_t row0 = tm * (128u * CTAS) + rank * 128u + quad * 32u;  // first row of this warp
+        const uint32_t row = row0 + lane;
+        const bool row_ok = row < p.m;
+        const uint32_t col_tile = tn * BN;
+        const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
+        if (row0 < p.m) {
+          for (uint32_t box = 0; box < BN / BOX_COLS; ++box) {
+            const uint32_t box_col = col_tile + box * BOX_COLS;
+            if (box_col >= p.n) break;
+            const uint32_t sb_addr = stg + sbuf * 4096u;
+            if (p.epilogue_tma) {
+              // The buffer about to be overwritten was handed to a TMA store two boxes ago.
+              if (lane == 0) ptx::bulk_wait_group_read<1>();
+              __syncwarp();
             }
-            sbuf ^= 1u;
+  #pragma unroll
+            for (int sl = 0; sl < SLICES; ++sl) {
+              const uint32_t col0 = box_col + sl * 32u;
+              if (col0 >= p.n) break;  // uniform across the warp
+              const uint32_t ncols = (p.n - col0 < 32u) ? (p.n - col0) : 32u;
+              uint32_t v[32];
+              ptx::tmem_ld_32x32(taddr + box * BOX_COLS + sl * 32u, v);
+              ptx::tmem_wait_ld();
+              const TOut* crow = cmat + static_cast<int64_t>(row) * p.ldc + col0;
+              detail::epilogue_math<TOut>(v, p, crow, row_ok, ncols);
+              if (p.epilogue_tma) {
+                // Row `lane` of the staged box; 16-byte chunk j lands at j ^ (lane % 8),
+                // the layout a 128B-swizzled tensor map expects.
+  #pragma unroll
+                for (int q = 0; q < WORDS / 4; ++q) {
+                  const uint32_t j = static_cast<uint32_t>(sl * (WORDS / 4) + q);
+                  const uint32_t addr = sb_addr + lane * 128u + ((j ^ (lane & 7u)) << 4);
+                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v[4 * q]),
+                               "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
+                               : "memory");
+                }
+              } else if (row_ok) {
+                TOut* drow = dmat + static_cast<int64_t>(row) * p.ldd + col0;
+                detail::store_direct<TOut>(v, drow, ncols, p.d_vec_ok != 0u);
+              }
+            }
+            if (p.epilogue_tma) {
+              ptx::fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                ptx::tma_store_2d(&tm_d, sb_addr, static_cast<int32_t>(box_col),
+                                  static_cast<int32_t>(row0));
+                ptx::bulk_commit_group();
+              }
+              sbuf ^= 1u;
+            }
           }
         }
       }
@@ -649,6 +850,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if (prof) {
       p.prof[16 * blockIdx.x + 5] = prof_wait;
       p.prof[16 * blockIdx.x + 6] = clock64() - prof_t0;
+      p.prof[16 * blockIdx.x + 12] = prof_park;
     }
   }
 

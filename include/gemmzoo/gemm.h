@@ -81,12 +81,23 @@ typedef enum gz_config {
   GZ_CFG_1CTA_N64 = 3,  /* 128x64 tile, one CTA  */
   GZ_CFG_2CTA_N256 = 4, /* 256x256 tile on a 2-CTA pair (tcgen05 cta_group::2) */
   GZ_CFG_2CTA_N128 = 5, /* 256x128 tile on a 2-CTA pair */
+  /* Skinny problems: operand roles exchanged, 128 output columns x up to 16/32/64/128 output rows per tile */
+  GZ_CFG_SWAP_M16 = 6,
+  GZ_CFG_SWAP_M32 = 7,
+  GZ_CFG_SWAP_M64 = 8,
+  GZ_CFG_SWAP_M128 = 9,
   GZ_CFG_SIMT = 15      /* plain CUDA-core kernel; chosen automatically when TMA alignment rules fail */
 } gz_config;
 
 /* flags */
 #define GZ_FLAG_EPILOGUE_DIRECT 0x1u /* registers -> global stores, no TMA store */
 #define GZ_FLAG_EPILOGUE_TMA 0x2u    /* force the shared-memory + TMA-store epilogue */
+/* Split-K (skinny problems only): the K range of a tile may be shared by several CTAs, which
+ * park fp32 partial sums in a workspace owned by the plan; the last CTA to arrive adds them in K
+ * order.  Chosen automatically when it balances the SMs better; these flags override the choice.
+ * A plan that uses the workspace must not run concurrently with itself on two streams. */
+#define GZ_FLAG_NO_SPLIT_K 0x4u
+#define GZ_FLAG_SPLIT_K 0x8u
 /* Test knob: the MMA warp never signals "accumulator ready", so the epilogue's
  * bounded wait expires and the launch reports GZ_ERR_DEVICE_TIMEOUT.  Nothing
  * faults or hangs; use with a small wait_limit_ns. */
@@ -118,7 +129,10 @@ typedef struct gz_plan_info {
   int32_t smem_bytes;   /* dynamic shared memory per CTA */
   int32_t epilogue_tma; /* 1 if the TMA-store epilogue is used */
   int32_t sm_count;
+  int32_t split_k;      /* 1 if K ranges are shared between CTAs (uses the plan's workspace) */
+  int32_t reserved;
   int64_t tiles;        /* output tiles */
+  int64_t workspace_bytes; /* device scratch memory owned by the plan */
   int64_t lda, ldb, ldc, ldd;
 } gz_plan_info;
 

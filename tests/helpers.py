@@ -188,7 +188,7 @@ def check(case: Case, device="cuda:0", rows=None):
     import torch
     a, b, c = make_operands(case)
     out, guard_ok, info, (status, detail) = run_gpu(case, a, b, c, device)
-    res = {"case": case.name(), "config": info.config, "epilogue_tma": info.epilogue_tma,
+    res = {"case": case.name(), "config": info.config, "epilogue_tma": info.epilogue_tma, "split_k": info.split_k,
            "guard_ok": guard_ok, "status": status, "detail": detail}
     ref = oracle_result(case, a, b, c, rows=rows, tf32_mode=0)
     got = out if rows is None else out[rows]

@@ -97,3 +97,71 @@ def test_many_tiles_persistent_loop():
     for config in (gz.CFG_1CTA_N64, gz.CFG_2CTA_N128):
         run(Case(BF16, BF16, 2048, 4096, 256, b_col=True, config=config))
     run(Case(S8, S32, 4096, 4096, 256, b_col=True, dist="full", config=gz.CFG_2CTA_N256))
+
+
+SWAP_CONFIGS = [(gz.CFG_SWAP_M16, 16), (gz.CFG_SWAP_M32, 32), (gz.CFG_SWAP_M64, 64), (gz.CFG_SWAP_M128, 128)]
+
+
+@pytest.mark.parametrize("config,mmax", SWAP_CONFIGS)
+@pytest.mark.parametrize("in_t,out_t", [(BF16, BF16), (F16, F32), (F32, F32), (S8, S32)])
+def test_swapped_operand_tiles(config, mmax, in_t, out_t):
+    """Skinny problems: B rides the 128-row side of the MMA, A the narrow side."""
+    dist = "full" if in_t == S8 else "int"
+    for m in sorted({1, mmax // 2 + 1, mmax}):
+        run(Case(in_t, out_t, m, 1000 if in_t != S8 else 1008, 512, b_col=True, config=config, dist=dist,
+                 alpha=2, beta=-1, pad_d=8))
+    # B row-major (N contiguous) on the wide side
+    run(Case(in_t, out_t, mmax, 640, 384, b_col=False, config=config, dist=dist, alpha=1, beta=1))
+
+
+def test_swapped_tiles_are_chosen_for_skinny_problems():
+    for m, want in ((1, gz.CFG_SWAP_M16), (16, gz.CFG_SWAP_M16), (17, gz.CFG_SWAP_M32)):
+        r = run(Case(BF16, BF16, m, 2048, 1024, b_col=True, dist="normal", beta=0.5, inplace=(m == 16)))
+        assert r["config"] == want
+    # A column-major with a narrow tile cannot be fetched in 128-byte chunks: falls back to a wide tile
+    r = run(Case(BF16, BF16, 16, 2048, 1024, a_col=True, b_col=True))
+    assert r["config"] not in (gz.CFG_SWAP_M16, gz.CFG_SWAP_M32, gz.CFG_SIMT)
+
+
+@pytest.mark.parametrize("in_t,out_t", [(BF16, BF16), (F16, F32), (F32, F32), (S8, S32)])
+@pytest.mark.parametrize("m,n,k", [(16, 14336, 4096), (5, 1000, 8192), (1, 136, 16384), (32, 4096, 2048),
+                                   (64, 640, 4096), (16, 128, 128 * 148 * 2), (100, 1024, 8192)])
+def test_split_k_last_arriver_reduction(in_t, out_t, m, n, k):
+    """K ranges shared between CTAs: partial sums parked in the plan's workspace, finished by the
+    last CTA to arrive.  Exact-integer inputs make the result independent of how K was cut."""
+    dist = "int"
+    if in_t == S8:
+        dist = "int"  # small values keep |sum| far below 2^31
+        n = -(-n // 16) * 16
+    config = (gz.CFG_SWAP_M16 if m <= 16 else gz.CFG_SWAP_M32 if m <= 32 else gz.CFG_SWAP_M64 if m <= 64
+              else gz.CFG_SWAP_M128)
+    r = run(Case(in_t, out_t, m, n, k, b_col=True, dist=dist, alpha=1, beta=1, config=config, flags=gz.FLAG_SPLIT_K))
+    assert r["split_k"] == 1
+
+
+def test_split_k_is_reproducible_and_reusable():
+    """Same plan called repeatedly (the arrival counters reset themselves) gives identical bits,
+    for random inputs too."""
+    import torch
+    m, n, k = 16, 4096, 4096   # 32 tiles for 148 SMs: the plan splits K on its own
+    a = torch.randn(m, k, device="cuda:0").bfloat16()
+    b = (torch.randn(n, k, device="cuda:0") * 0.02).bfloat16()
+    g = gz.Sm100Gemm(m, n, k, BF16, BF16, layout_b=gz.COL_MAJOR)
+    assert g.info().split_k == 1 and g.info().workspace_bytes > 0 and g.info().grid > 32
+    outs = []
+    for _ in range(4):
+        d = torch.empty(m, n, dtype=torch.bfloat16, device="cuda:0")
+        g(a, b, None, d, 1.0, 0.0)
+        outs.append(d)
+    torch.cuda.synchronize()
+    assert g.plan.device_status()[0] == 0
+    for d in outs[1:]:
+        assert torch.equal(d.view(torch.int16), outs[0].view(torch.int16))
+    ref = (a.double() @ b.double().t())
+    assert ((outs[0].double() - ref).abs() <= 2.0 ** -8 * ref.abs() + 1e-3).all()
+    # and agrees with the unsplit kernel to within fp32 summation-order effects
+    d2 = torch.empty(m, n, dtype=torch.float32, device="cuda:0")
+    d3 = torch.empty_like(d2)
+    gz.Sm100Gemm(m, n, k, BF16, gz.DT_F32, layout_b=gz.COL_MAJOR, flags=gz.FLAG_NO_SPLIT_K)(a, b, None, d2, 1.0, 0.0)
+    gz.Sm100Gemm(m, n, k, BF16, gz.DT_F32, layout_b=gz.COL_MAJOR, flags=gz.FLAG_SPLIT_K)(a, b, None, d3, 1.0, 0.0)
+    assert ((d2 - d3).abs() <= 1e-4).all()
