@@ -25,7 +25,7 @@ GZ_ERR_DEVICE_TIMEOUT, GZ_ERR_NO_DEVICE, GZ_ERR_TOO_LARGE, GZ_ERR_OUT_OF_MEMORY 
 EXPORTED_SYMBOLS = [
     "gz_gemm_desc_validate", "gz_gemm_plan_create", "gz_gemm_plan_destroy", "gz_gemm_plan_info",
     "gz_gemm_plan_set_profile",
-    "gz_gemm_run", "gz_gemm_run_host", "gz_last_device_status", "gz_status_string",
+    "gz_gemm_run", "gz_gemm_run_host", "gz_gemm_skinny_static", "gz_last_device_status", "gz_status_string",
     "gz_last_cuda_error", "gz_fill", "gz_tile_coords", "gz_partition_columns", "gz_version",
 ]
 
@@ -109,6 +109,8 @@ def lib():
     L.gz_gemm_plan_set_profile.restype = C.c_int
     L.gz_gemm_run_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp]
     L.gz_gemm_run_host.restype = C.c_int
+    L.gz_gemm_skinny_static.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, vp]
+    L.gz_gemm_skinny_static.restype = C.c_int
     L.gz_last_device_status.argtypes = [vp, vp, C.POINTER(u32 * 4)]
     L.gz_last_device_status.restype = C.c_int
     L.gz_status_string.argtypes = [C.c_int]
@@ -266,6 +268,17 @@ class Sm100Gemm:
 
     def info(self):
         return self.plan.info()
+
+
+STATIC_SCRATCH_BYTES = 8 << 20
+
+
+def gemm_skinny_static(desc: GemmDesc, a, b, c, d, alpha, beta, stream=None):
+    """gz_gemm_skinny_static: the skinny split-K GEMM with its scratch in the library's fixed
+    array, for hosts that must not allocate.  Returns the gz_status (0 = launched)."""
+    al, be = _scalar(desc.in_type, alpha), _scalar(desc.in_type, beta)
+    return lib().gz_gemm_skinny_static(C.byref(desc), _ptr(a), _ptr(b), _ptr(c), _ptr(d), C.byref(al),
+                                       C.byref(be), _stream_handle(stream))
 
 
 def fill(t, seed, stream_id, dist, scale=1.0, stream=None):

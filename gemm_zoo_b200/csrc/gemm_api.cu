@@ -912,3 +912,167 @@ extern "C" GZ_API gz_status gz_fill(void* ptr, int32_t dtype, int64_t count, uin
   if (!cuda_ok(cudaGetLastError(), "fill launch")) return GZ_ERR_CUDA;
   return GZ_OK;
 }
+
+// ------------------------------------------------------------------ no-allocation entry point
+//
+// Some hosts hand all device memory to their own allocator at start-up and forbid any later
+// cudaMalloc: it could fail against their budget, and it synchronises the device in the middle of
+// a latency-critical loop.  Such a host cannot use gz_gemm_plan_create (which allocates the plan's
+// status words and split-K workspace).  For it, the skinny split-K GEMM is offered once more with
+// its scratch memory in a fixed array that is part of the library image: every GPU that loads the
+// library holds GZ_STATIC_SCRATCH_BYTES of it until the process exits.
+namespace {
+
+static __device__ __align__(256) unsigned char g_static_scratch[GZ_STATIC_SCRATCH_BYTES];
+
+struct StaticScratchDevice {
+  void* ptr = nullptr;  // device address of g_static_scratch on this device
+  int sm_count = 0;
+  bool ready = false;
+};
+constexpr int kMaxDevices = 64;
+StaticScratchDevice g_static_dev[kMaxDevices];
+std::mutex g_static_mu;
+
+// Once per device, with that device current: the array's name is only a host-side handle, the
+// kernel needs the address cudaGetSymbolAddress reports for the current device.
+gz_status static_scratch_setup(int device, StaticScratchDevice** out) {
+  if (device < 0 || device >= kMaxDevices) return GZ_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  StaticScratchDevice& sd = g_static_dev[device];
+  if (!sd.ready) {
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+      (void)cudaGetLastError();
+      return GZ_ERR_NO_DEVICE;
+    }
+    if (device >= ndev) return GZ_ERR_INVALID_ARG;
+    int major = 0, sms = 0;
+    if (!cuda_ok(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device), "device attribute") ||
+        !cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "device attribute"))
+      return GZ_ERR_CUDA;
+    if (major != 10) return GZ_ERR_NO_DEVICE;
+    if (!cuda_ok(cudaSetDevice(device), "cudaSetDevice")) return GZ_ERR_CUDA;
+    void* ptr = nullptr;
+    if (!cuda_ok(cudaGetSymbolAddress(&ptr, g_static_scratch), "cudaGetSymbolAddress(static scratch)") || !ptr)
+      return GZ_ERR_CUDA;
+    sd.ptr = ptr;
+    sd.sm_count = sms;
+    sd.ready = true;
+  }
+  *out = &sd;
+  return GZ_OK;
+}
+
+}  // namespace
+
+extern "C" GZ_API gz_status gz_gemm_skinny_static(const gz_gemm_desc* desc, const void* a, const void* b,
+                                                  const void* c, void* d, const void* alpha,
+                                                  const void* beta, void* stream_v) {
+  if (!desc || !a || !b || !d) return GZ_ERR_INVALID_ARG;
+  gz_gemm_desc dd = *desc;
+  if (dd.struct_size != sizeof(gz_gemm_desc)) return GZ_ERR_INVALID_ARG;
+  dd.flags = (dd.flags & ~GZ_FLAG_NO_SPLIT_K) | GZ_FLAG_SPLIT_K | GZ_FLAG_EPILOGUE_DIRECT;
+  dd.flags &= ~GZ_FLAG_EPILOGUE_TMA;
+  Problem pr;
+  gz_status st = normalise(&dd, &pr);
+  if (st != GZ_OK) return st;
+  if (pr.d.m > 128) return GZ_ERR_UNSUPPORTED;  // only the skinny (swapped-operand) kernel uses scratch
+  if (!pr.tma_ld_ok) return GZ_ERR_MISALIGNED;
+  auto misaligned = [](const void* p, int sz) { return (reinterpret_cast<uintptr_t>(p) % sz) != 0; };
+  if (misaligned(a, 16) || misaligned(b, 16) || misaligned(d, pr.out_size) || (c && misaligned(c, pr.out_size)))
+    return GZ_ERR_MISALIGNED;
+  float af, bf;
+  int32_t ai, bi;
+  st = read_scalars(pr, alpha, beta, &af, &bf, &ai, &bi);
+  if (st != GZ_OK) return st;
+  const bool beta_zero = (pr.d.in_type == GZ_DT_S8) ? (bi == 0) : (bf == 0.0f);
+  if (!beta_zero && !c) return GZ_ERR_INVALID_ARG;
+
+  StaticScratchDevice* sd = nullptr;
+  st = static_scratch_setup(pr.d.device, &sd);
+  if (st != GZ_OK) return st;
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess || cur != pr.d.device) {
+    if (!cuda_ok(cudaSetDevice(pr.d.device), "cudaSetDevice")) return GZ_ERR_CUDA;
+  }
+
+  int config = pr.d.config;
+  if (config == GZ_CFG_AUTO)
+    config = pr.d.m <= 16 ? GZ_CFG_SWAP_M16 : pr.d.m <= 32 ? GZ_CFG_SWAP_M32 : pr.d.m <= 64 ? GZ_CFG_SWAP_M64
+                                                                                            : GZ_CFG_SWAP_M128;
+  const CfgShape* sp = shape_of(config);
+  if (!sp || !sp->swap) return GZ_ERR_UNSUPPORTED;
+  const CfgShape& s = *sp;
+  if (!shape_fits(pr, s)) return GZ_ERR_UNSUPPORTED;
+  gz_plan_info info;
+  fill_info(pr, config, sd->sm_count, &info);
+  if (!info.split_k) return GZ_ERR_UNSUPPORTED;  // a single K block in total: nothing to share
+  constexpr size_t kStatusBytes = 256;
+  if ((size_t)info.workspace_bytes + kStatusBytes > (size_t)GZ_STATIC_SCRATCH_BYTES) {
+    char buf[160];
+    std::snprintf(buf, sizeof(buf), "static scratch too small: this problem needs %lld bytes, the library holds %u",
+                  (long long)info.workspace_bytes + (long long)kStatusBytes, (unsigned)GZ_STATIC_SCRATCH_BYTES);
+    g_last_cuda_error = buf;
+    return GZ_ERR_TOO_LARGE;
+  }
+  const KernelEntry entry = entry_for(pr.d.in_type, pr.d.out_type, config);
+  if (!entry.launch) return GZ_ERR_UNSUPPORTED;
+  if (!cuda_ok(entry.attr(), "cudaFuncSetAttribute(max dynamic shared memory)")) return GZ_ERR_CUDA;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  unsigned char* base = static_cast<unsigned char*>(sd->ptr);
+  const size_t ws_bytes = (size_t)info.workspace_bytes;
+  gz::GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  build_operand(&p.a, pr.b_mn_major, 128, pr.in_size);
+  build_operand(&p.b, pr.a_mn_major, s.bn, pr.in_size);
+  p.grid.tiles_m = (uint32_t)cdiv(pr.d.n, 128);
+  p.grid.tiles_n = (uint32_t)cdiv(pr.d.m, s.bn);
+  p.grid.group_m = 16;
+  p.grid.num_tiles = p.grid.tiles_m * p.grid.tiles_n;
+  p.m = (uint32_t)pr.d.n;
+  p.n = (uint32_t)pr.d.m;
+  p.k = (uint32_t)pr.d.k;
+  p.bk = 128u / pr.in_size;
+  p.k_blocks = (uint32_t)cdiv(pr.d.k, p.bk);
+  p.idesc = build_idesc(pr, s);
+  p.epilogue_tma = 0;
+  p.ldc = pr.d.ldc;
+  p.ldd = pr.d.ldd;
+  p.wait_limit_ns = pr.d.wait_limit_ns;
+  p.alpha_f = af;
+  p.beta_f = bf;
+  p.alpha_i = ai;
+  p.beta_i = bi;
+  p.c = beta_zero ? nullptr : c;
+  p.d = d;
+  p.split_k = 1;
+  p.max_contrib = (uint32_t)info.reserved;
+  p.total_kb = (unsigned long long)p.grid.num_tiles * p.k_blocks;
+  const size_t counter_bytes = (size_t)p.grid.num_tiles * 4;
+  p.ws = reinterpret_cast<float*>(base);
+  p.counters = reinterpret_cast<int*>(base + (ws_bytes - counter_bytes));
+  p.status = reinterpret_cast<uint32_t*>(base + (GZ_STATIC_SCRATCH_BYTES - kStatusBytes));
+  // The array keeps whatever the last call left in it.  The partial sums are always written before
+  // they are read; the arrival counters and the status words must start at zero.
+  if (!cuda_ok(cudaMemsetAsync(p.counters, 0, counter_bytes, stream), "clear arrival counters") ||
+      !cuda_ok(cudaMemsetAsync(p.status, 0, kStatusBytes, stream), "clear status words"))
+    return GZ_ERR_CUDA;
+
+  CUtensorMap ta, tb;
+  const uint32_t bk = p.bk;
+  auto encode_input = [&](CUtensorMap* tm, const void* ptr, bool mn_major, int64_t rows, int64_t ld,
+                          const gz::OperandDesc& od) {
+    if (!mn_major)
+      return encode_2d(tm, pr.d.in_type, ptr, (uint64_t)pr.d.k, (uint64_t)rows, (uint64_t)ld * pr.in_size, bk,
+                       od.box_mn, true);
+    return encode_2d(tm, pr.d.in_type, ptr, (uint64_t)rows, (uint64_t)pr.d.k, (uint64_t)ld * pr.in_size,
+                     od.box_mn, bk, true, pr.in_size == 4);
+  };
+  if (!encode_input(&ta, b, pr.b_mn_major, pr.d.n, pr.d.ldb, p.a) ||
+      !encode_input(&tb, a, pr.a_mn_major, pr.d.m, pr.d.lda, p.b))
+    return GZ_ERR_CUDA;
+  if (!cuda_ok(entry.launch(ta, tb, ta, p, info.grid, stream), "kernel launch")) return GZ_ERR_CUDA;
+  return GZ_OK;
+}

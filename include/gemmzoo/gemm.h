@@ -163,6 +163,28 @@ GZ_API gz_status gz_gemm_run(gz_plan* plan, const void* a, const void* b, const 
 GZ_API gz_status gz_gemm_run_host(gz_plan* plan, const void* a, const void* b, const void* c, void* d,
                                   const void* alpha, const void* beta, void* stream);
 
+/* The same skinny (M <= 128) split-K GEMM for hosts that must not allocate.  This entry point has
+ * no counterpart in the reference.  It exists for callers that gave all device memory to their own
+ * allocator at start-up and may not call cudaMalloc afterwards (it could fail against their budget
+ * and it synchronises the device inside a latency-critical loop), so they cannot create a plan.
+ * Nothing is allocated here, neither on the device nor through any allocating library routine:
+ * the partial sums, arrival counters and status words of the kernel live in a fixed array inside
+ * the library image, GZ_STATIC_SCRATCH_BYTES per GPU that loads the library, held until exit.
+ *   - `desc` describes the problem as for gz_gemm_plan_create; a, b, c, d are device pointers that
+ *     TMA can address (16-byte aligned A and B, leading dimensions sized in multiples of 16 bytes).
+ *     GZ_ERR_UNSUPPORTED for m > 128, GZ_ERR_MISALIGNED for operands TMA cannot describe.
+ *   - A problem whose partial sums do not fit the array is refused with GZ_ERR_TOO_LARGE
+ *     (gz_last_cuda_error() then says how many bytes it needs); use a plan for it.
+ *   - The first call on a device looks up the array's device address and opts the kernel into its
+ *     shared-memory size; make that first call before any stream capture.
+ *   - Every call on a device shares the one array.  It keeps the previous call's contents; what
+ *     must start at zero is cleared on `stream` before the launch.  Two calls that overlap on the
+ *     GPU (different streams, or different threads) race on it: serialise them.
+ * Asynchronous on `stream`. */
+#define GZ_STATIC_SCRATCH_BYTES (8u << 20)
+GZ_API gz_status gz_gemm_skinny_static(const gz_gemm_desc* desc, const void* a, const void* b, const void* c,
+                                       void* d, const void* alpha, const void* beta, void* stream);
+
 /* Synchronises the plan's device status word: returns GZ_OK, or
  * GZ_ERR_DEVICE_TIMEOUT if a bounded wait expired in any launch since the last
  * call (detail[0] = role/barrier code, detail[1] = block, detail[2] = tile,
