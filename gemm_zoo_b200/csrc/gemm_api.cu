@@ -167,6 +167,27 @@ bool wants_split_k(const Problem& pr, const CfgShape& s, int sm_count) {
   return tiles * 2 <= sm_count && total >= (int64_t)sm_count * 4;
 }
 
+// Tail splitting for whole-tile schedules: if the last wave would fill at most half (a quarter) of
+// the SMs, its tiles are cut into 2 (4) column strips so that the wave is short instead of sparse.
+// Returns the number of strips per tail tile (1 = none) and sets *first to the first tail tile.
+int tail_parts_for(const Problem& pr, const CfgShape& s, int64_t tiles, int64_t units, int64_t* first) {
+  *first = tiles;
+  if (s.swap || units <= 0 || tiles <= units) return 1;  // a single (partial) wave is not split
+  const int64_t rem = tiles % units;
+  if (rem == 0) return 1;
+  const int chunk = 128 / pr.in_size;
+  int parts = 1;
+  for (int f = 2; f <= 4; f *= 2) {
+    const int strip = s.bn / f;                      // columns per strip
+    if (strip < 64 || rem * f > units) break;
+    if (pr.b_mn_major && (strip / s.ctas) % chunk != 0) break;  // N-contiguous B is fetched in 128-byte chunks
+    if ((strip / s.ctas) % 8 != 0) break;
+    parts = f;
+  }
+  if (parts > 1) *first = tiles - rem;
+  return parts;
+}
+
 // Pick the tile shape with the least estimated time.  Per 128-byte K block a CTA is held up by
 // the slowest of: the MMAs (a 128 x bn x 32-byte MMA takes bn/2 cycles, four per block), the
 // L2 -> shared-memory fill of its stage (about 64 bytes per cycle per SM), and the issue cost of
@@ -188,9 +209,16 @@ int choose_config(const Problem& pr, int sm_count) {
     const double issue = 250.0;
     double per_block = mma > fill ? mma : fill;
     if (issue > per_block) per_block = issue;
-    const int64_t blocks_per_cta =
-        wants_split_k(pr, s, sm_count) ? cdiv(tiles * k_blocks, units) : cdiv(tiles, units) * k_blocks;
-    const double cost = double(blocks_per_cta) * per_block;
+    double blocks_per_cta;
+    if (wants_split_k(pr, s, sm_count)) {
+      blocks_per_cta = double(cdiv(tiles * k_blocks, units));
+    } else {
+      int64_t first;
+      const int parts = tail_parts_for(pr, s, tiles, units, &first);
+      const double waves = parts > 1 ? double(first / units) + 1.0 / parts : double(cdiv(tiles, units));
+      blocks_per_cta = waves * double(k_blocks);
+    }
+    const double cost = blocks_per_cta * per_block;
     if (best == 0 || cost < best) {
       best = cost;
       best_cfg = s.config;
@@ -610,12 +638,24 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
     uint32_t gm = 2048u / tile_m;
     p.grid.group_m = gm < 1 ? 1 : gm;
     p.grid.num_tiles = p.grid.tiles_m * p.grid.tiles_n;
+    {
+      int64_t first;
+      const int parts = tail_parts_for(pr, s, p.grid.num_tiles, sm_count / s.ctas, &first);
+      p.tail_first = (uint32_t)first;
+      p.tail_parts = (uint32_t)parts;
+      p.virt_tiles = (uint32_t)(first + (p.grid.num_tiles - first) * parts);
+    }
     p.m = (uint32_t)wide;
     p.n = (uint32_t)narrow;
     p.k = (uint32_t)pr.d.k;
     p.bk = 128u / pr.in_size;
     p.k_blocks = (uint32_t)cdiv(pr.d.k, p.bk);
     p.idesc = build_idesc(pr, s);
+    {
+      CfgShape strip = s;
+      strip.bn = s.bn / (int)p.tail_parts;
+      p.idesc_tail = build_idesc(pr, strip);
+    }
     p.epilogue_tma = pl->info.epilogue_tma;
     p.test_flags = (pr.d.flags & 0x80000000u) ? 1u : 0u;
     // Developer tuning knobs, read once per plan.
@@ -1031,6 +1071,9 @@ extern "C" GZ_API gz_status gz_gemm_skinny_static(const gz_gemm_desc* desc, cons
   p.grid.tiles_n = (uint32_t)cdiv(pr.d.m, s.bn);
   p.grid.group_m = 16;
   p.grid.num_tiles = p.grid.tiles_m * p.grid.tiles_n;
+  p.tail_first = p.grid.num_tiles;
+  p.tail_parts = 1;
+  p.virt_tiles = p.grid.num_tiles;
   p.m = (uint32_t)pr.d.n;
   p.n = (uint32_t)pr.d.m;
   p.k = (uint32_t)pr.d.k;

@@ -83,6 +83,11 @@ struct GemmParams {
   void* d;
   uint32_t* status;  // 4 words in global memory
   uint64_t wait_limit_ns;
+  // Tail splitting (whole-tile mode only): tiles [tail_first, num_tiles) — the ones that would form a
+  // last, mostly empty wave — are each cut into tail_parts column strips of BN / tail_parts columns,
+  // so that the last wave is short instead of sparse.  virt_tiles counts whole tiles plus strips.
+  uint32_t tail_first, tail_parts, virt_tiles;
+  uint32_t idesc_tail;  // instruction descriptor with N = BN / tail_parts
   // Split-K work distribution (0 = whole tiles, dealt round-robin).  When set, the K blocks of all
   // tiles form one line that is cut into equal contiguous ranges, one per CTA; a tile whose K range
   // is shared by several CTAs is finished by whichever of them arrives last (see the epilogue).
@@ -198,12 +203,15 @@ __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, const Abort&
 // The sequence of (tile, K-block range) pieces one CTA (or CTA pair) works through.  Every role
 // of the CTA constructs the same iterator and so sees the same sequence.
 struct WorkIter {
-  uint32_t k_blocks, num_tiles, step, next_tile;
+  uint32_t k_blocks, virt_tiles, tail_first, tail_parts, bn, step, next_tile;
+  uint32_t col_off, cols;  // column strip of the tile the current piece covers
   unsigned long long cur, end;
   bool split;
-  __device__ __forceinline__ WorkIter(const GemmParams& p, uint32_t cluster, uint32_t num_clusters)
-      : k_blocks(p.k_blocks), num_tiles(p.grid.num_tiles), step(num_clusters), next_tile(cluster),
-        cur(0), end(0), split(p.split_k != 0u) {
+  __device__ __forceinline__ WorkIter(const GemmParams& p, uint32_t cluster, uint32_t num_clusters,
+                                      uint32_t tile_cols)
+      : k_blocks(p.k_blocks), virt_tiles(p.virt_tiles), tail_first(p.tail_first),
+        tail_parts(p.tail_parts), bn(tile_cols), step(num_clusters), next_tile(cluster), col_off(0),
+        cols(tile_cols), cur(0), end(0), split(p.split_k != 0u) {
     if (split) {
       cur = static_cast<unsigned long long>(cluster) * p.total_kb / num_clusters;
       end = static_cast<unsigned long long>(cluster + 1u) * p.total_kb / num_clusters;
@@ -211,8 +219,17 @@ struct WorkIter {
   }
   __device__ __forceinline__ bool next(uint32_t& tile, uint32_t& kb_lo, uint32_t& kb_hi) {
     if (!split) {
-      if (next_tile >= num_tiles) return false;
-      tile = next_tile;
+      if (next_tile >= virt_tiles) return false;
+      if (next_tile < tail_first) {
+        tile = next_tile;
+        col_off = 0;
+        cols = bn;
+      } else {
+        const uint32_t sub = next_tile - tail_first;
+        tile = tail_first + sub / tail_parts;
+        cols = bn / tail_parts;
+        col_off = (sub % tail_parts) * cols;
+      }
       kb_lo = 0;
       kb_hi = k_blocks;
       next_tile += step;
@@ -471,12 +488,12 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     bool ok = true;
     long long prof_wait = 0, prof_issue = 0;
     const long long prof_t0 = PROF ? clock64() : 0;
-    detail::WorkIter work(p, cluster, num_clusters);
+    detail::WorkIter work(p, cluster, num_clusters, BN);
     uint32_t t = 0, kb_lo = 0, kb_hi = 0;
     while (ok && work.next(t, kb_lo, kb_hi)) {
       uint32_t tm, tn;
       tile_coords(p.grid, t, tm, tn);
-      const int32_t row0 = is_b ? static_cast<int32_t>(tn * BN + rank * Cfg::BN_CTA)
+      const int32_t row0 = is_b ? static_cast<int32_t>(tn * BN + work.col_off + rank * (work.cols / CTAS))
                                 : static_cast<int32_t>(tm * (128u * CTAS) + rank * 128u);
       for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
         const long long w0 = PROF ? clock64() : 0;
@@ -557,7 +574,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint32_t b_lo0 = (((base + Cfg::A_BYTES) >> 4) & 0x3FFFu) | p.b.desc_lo;
       const uint32_t a_step = p.a.k_step16, b_step = p.b.k_step16;
       const uint32_t idesc = p.idesc;
-      detail::WorkIter work(p, cluster, num_clusters);
+      detail::WorkIter work(p, cluster, num_clusters, BN);
       uint32_t t = 0, kb_lo = 0, kb_hi = 0;
       while (ok && work.next(t, kb_lo, kb_hi)) {
         const long long w0 = PROF ? clock64() : 0;
@@ -568,6 +585,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if constexpr (PROF) prof_tmem += clock64() - w0;
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t idesc_cur = (work.cols == static_cast<uint32_t>(BN)) ? idesc : p.idesc_tail;
         for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
           const long long w1 = PROF ? clock64() : 0;
           const bool got = detail::wait(full_bar(stage), phase, ab, WAIT_MMA_FULL, t, kb);
@@ -583,7 +601,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             for (uint32_t j = 0; j < 4; ++j) {  // 128 bytes of K per stage, 32 bytes per MMA
               const uint64_t ad = (static_cast<uint64_t>(a_hi) << 32) | (a_lo + j * a_step);
               const uint64_t bd = (static_cast<uint64_t>(b_hi) << 32) | (b_lo + j * b_step);
-              ptx::umma<Cfg::KIND, CTAS>(d_tmem, ad, bd, idesc, (kb != kb_lo || j != 0u) ? 1u : 0u);
+              ptx::umma<Cfg::KIND, CTAS>(d_tmem, ad, bd, idesc_cur, (kb != kb_lo || j != 0u) ? 1u : 0u);
             }
             // Release the stage to the producer(s) once these MMAs have read it.
             if constexpr (CTAS == 2) {
@@ -657,7 +675,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     TOut* const dmat = static_cast<TOut*>(p.d);
     const uint32_t tmem_empty_target =
         (CTAS == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
-    detail::WorkIter work(p, cluster, num_clusters);
+    detail::WorkIter work(p, cluster, num_clusters, BN);
     uint32_t t = 0, kb_lo = 0, kb_hi = 0;
     while (ok && work.next(t, kb_lo, kb_hi)) {
       uint32_t tm, tn;
@@ -788,10 +806,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const uint32_t row0 = tm * (128u * CTAS) + rank * 128u + quad * 32u;  // first row of this warp
         const uint32_t row = row0 + lane;
         const bool row_ok = row < p.m;
-        const uint32_t col_tile = tn * BN;
+        const uint32_t col_tile = tn * BN + work.col_off;
         const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
         if (row0 < p.m) {
-          for (uint32_t box = 0; box < BN / BOX_COLS; ++box) {
+          for (uint32_t box = 0; box < work.cols / BOX_COLS; ++box) {
             const uint32_t box_col = col_tile + box * BOX_COLS;
             if (box_col >= p.n) break;
             const uint32_t sb_addr = stg + sbuf * 4096u;

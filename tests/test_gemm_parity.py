@@ -165,3 +165,18 @@ def test_split_k_is_reproducible_and_reusable():
     gz.Sm100Gemm(m, n, k, BF16, gz.DT_F32, layout_b=gz.COL_MAJOR, flags=gz.FLAG_NO_SPLIT_K)(a, b, None, d2, 1.0, 0.0)
     gz.Sm100Gemm(m, n, k, BF16, gz.DT_F32, layout_b=gz.COL_MAJOR, flags=gz.FLAG_SPLIT_K)(a, b, None, d3, 1.0, 0.0)
     assert ((d2 - d3).abs() <= 1e-4).all()
+
+
+@pytest.mark.parametrize("config,m,n", [(gz.CFG_2CTA_N256, 1536, 3584),   # 84 tiles on 74 pairs: 10 tail tiles in 4 strips
+                                        (gz.CFG_2CTA_N256, 2048, 3328),   # 104 tiles: 30 tail tiles in 2 strips
+                                        (gz.CFG_1CTA_N256, 2048, 2560 + 256),  # 176 tiles on 148 CTAs
+                                        (gz.CFG_1CTA_N128, 2176, 1280),   # 170 tiles: 22 tail tiles, 2 strips of 64
+                                        (gz.CFG_2CTA_N128, 2560, 1024 + 128)])
+@pytest.mark.parametrize("in_t,out_t,b_col", [(BF16, BF16, True), (BF16, F32, False), (F32, F32, False),
+                                              (S8, S32, True)])
+def test_tail_wave_is_cut_into_column_strips(config, m, n, in_t, out_t, b_col):
+    """Problems whose last wave of tiles would be mostly empty: those tiles are computed as narrower
+    column strips.  Results must not change."""
+    dist = "full" if in_t == S8 else "int"
+    run(Case(in_t, out_t, m, n, 256, b_col=b_col, config=config, dist=dist, alpha=2, beta=1))
+    run(Case(in_t, out_t, m - 8, n - 24, 192, b_col=b_col, config=config, dist=dist, alpha=1, beta=0))
