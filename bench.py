@@ -23,7 +23,7 @@ Keys beyond the base contract:
   e2e           same metric through gz_gemm_run_host with pinned HOST operands: H2D of A
                 and B and D2H of D inside the timed region
   cublaslt      cuBLASLt on the same operands in the same process, interleaved
-  other_dtypes  fp16 / tf32 / s8 at 8192^3 and the bf16 4096^3 beta=0.5 config (own | cuBLASLt)
+  other_dtypes  fp16 / tf32 / s8 / fp8 at 8192^3 and the bf16 4096^3 beta=0.5 config (own | cuBLASLt)
 """
 from __future__ import annotations
 
@@ -380,6 +380,7 @@ def other_dtypes(gz, torch, dev, stream):
         ("tf32_8192_rowrow", gz.DT_F32, gz.DT_F32, torch.float32, torch.float32, 8192, gz.ROW_MAJOR, 1.0, 0.0),
         ("s8_8192", gz.DT_S8, gz.DT_S32, torch.int8, torch.int32, 8192, gz.COL_MAJOR, 1, 0),
         ("bf16_4096_beta0.5", gz.DT_BF16, gz.DT_BF16, torch.bfloat16, torch.bfloat16, 4096, gz.COL_MAJOR, 1.0, 0.5),
+        ("e4m3_8192_bf16out", gz.DT_E4M3, gz.DT_BF16, torch.float8_e4m3fn, torch.bfloat16, 8192, gz.COL_MAJOR, 1.0, 0.0),
     ]
     for name, it, ot, tin, tout, sz, lb, alpha, beta in cases:
         sets = 2 if sz == 8192 else 4

@@ -10,7 +10,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 
 # enums (mirror gemm.h)
-DT_F16, DT_BF16, DT_F32, DT_S8, DT_S32 = 0, 1, 2, 3, 4
+DT_F16, DT_BF16, DT_F32, DT_S8, DT_S32, DT_E4M3, DT_E5M2 = 0, 1, 2, 3, 4, 5, 6
 ROW_MAJOR, COL_MAJOR = 0, 1
 CFG_AUTO, CFG_1CTA_N256, CFG_1CTA_N128, CFG_1CTA_N64, CFG_2CTA_N256, CFG_2CTA_N128, CFG_SIMT = 0, 1, 2, 3, 4, 5, 15
 CFG_SWAP_M16, CFG_SWAP_M32, CFG_SWAP_M64, CFG_SWAP_M128 = 6, 7, 8, 9
@@ -243,7 +243,8 @@ def _torch_dtype_code(t):
     if _TORCH_DT is None:
         import torch
         _TORCH_DT = {torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.float32: DT_F32,
-                     torch.int8: DT_S8, torch.int32: DT_S32}
+                     torch.int8: DT_S8, torch.int32: DT_S32, torch.float8_e4m3fn: DT_E4M3,
+                     torch.float8_e5m2: DT_E5M2}
     return _TORCH_DT[t]
 
 

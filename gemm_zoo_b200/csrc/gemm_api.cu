@@ -9,6 +9,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include <cmath>
@@ -62,15 +63,20 @@ int dtype_size(int dt) {
     case GZ_DT_BF16: return 2;
     case GZ_DT_F32:
     case GZ_DT_S32: return 4;
-    case GZ_DT_S8: return 1;
+    case GZ_DT_S8:
+    case GZ_DT_E4M3:
+    case GZ_DT_E5M2: return 1;
   }
   return 0;
 }
 
+bool is_fp8(int dt) { return dt == GZ_DT_E4M3 || dt == GZ_DT_E5M2; }
+
 bool pair_supported(int in, int out) {
   return (in == GZ_DT_F16 && (out == GZ_DT_F16 || out == GZ_DT_F32)) ||
          (in == GZ_DT_BF16 && (out == GZ_DT_BF16 || out == GZ_DT_F32)) ||
-         (in == GZ_DT_F32 && out == GZ_DT_F32) || (in == GZ_DT_S8 && out == GZ_DT_S32);
+         (in == GZ_DT_F32 && out == GZ_DT_F32) || (in == GZ_DT_S8 && out == GZ_DT_S32) ||
+         (is_fp8(in) && (out == GZ_DT_F16 || out == GZ_DT_BF16 || out == GZ_DT_F32));
 }
 
 struct CfgShape {
@@ -365,6 +371,9 @@ KernelEntry entry_for(int in, int out, int config) {
     return entry_for_shape<Kind::F16, float>(config);
   if (in == GZ_DT_F32) return entry_for_shape<Kind::TF32, float>(config);
   if (in == GZ_DT_S8) return entry_for_shape<Kind::I8, int32_t>(config);
+  if (is_fp8(in) && out == GZ_DT_F16) return entry_for_shape<Kind::F8, __half>(config);
+  if (is_fp8(in) && out == GZ_DT_BF16) return entry_for_shape<Kind::F8, __nv_bfloat16>(config);
+  if (is_fp8(in) && out == GZ_DT_F32) return entry_for_shape<Kind::F8, float>(config);
   return {nullptr, nullptr, nullptr, nullptr};
 }
 
@@ -383,6 +392,12 @@ cudaError_t launch_simt_any(int in, int out, const gz::SimtParams& sp, cudaStrea
   if (in == GZ_DT_BF16 && out == GZ_DT_F32) return launch_simt<__nv_bfloat16, float>(sp, stream);
   if (in == GZ_DT_F32) return launch_simt<float, float>(sp, stream);
   if (in == GZ_DT_S8) return launch_simt<int8_t, int32_t>(sp, stream);
+  if (in == GZ_DT_E4M3 && out == GZ_DT_F16) return launch_simt<__nv_fp8_e4m3, __half>(sp, stream);
+  if (in == GZ_DT_E4M3 && out == GZ_DT_BF16) return launch_simt<__nv_fp8_e4m3, __nv_bfloat16>(sp, stream);
+  if (in == GZ_DT_E4M3 && out == GZ_DT_F32) return launch_simt<__nv_fp8_e4m3, float>(sp, stream);
+  if (in == GZ_DT_E5M2 && out == GZ_DT_F16) return launch_simt<__nv_fp8_e5m2, __half>(sp, stream);
+  if (in == GZ_DT_E5M2 && out == GZ_DT_BF16) return launch_simt<__nv_fp8_e5m2, __nv_bfloat16>(sp, stream);
+  if (in == GZ_DT_E5M2 && out == GZ_DT_F32) return launch_simt<__nv_fp8_e5m2, float>(sp, stream);
   return cudaErrorInvalidValue;
 }
 
@@ -478,6 +493,8 @@ uint32_t build_idesc(const Problem& pr, const CfgShape& s) {
     case GZ_DT_F16: fmt_ab = 0; fmt_c = 1; break;
     case GZ_DT_BF16: fmt_ab = 1; fmt_c = 1; break;
     case GZ_DT_F32: fmt_ab = 2; fmt_c = 1; break;  // tf32 operands, f32 accumulate
+    case GZ_DT_E4M3: fmt_ab = 0; fmt_c = 1; break;
+    case GZ_DT_E5M2: fmt_ab = 1; fmt_c = 1; break;
     default: fmt_ab = 1; fmt_c = 2; break;         // signed 8-bit operands, s32 accumulate
   }
   uint32_t idesc = 0;
@@ -887,6 +904,10 @@ __device__ __forceinline__ __nv_bfloat16 fill_cast<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
 }
 template <>
+__device__ __forceinline__ __nv_fp8_e4m3 fill_cast<__nv_fp8_e4m3>(float v) { return __nv_fp8_e4m3(v); }
+template <>
+__device__ __forceinline__ __nv_fp8_e5m2 fill_cast<__nv_fp8_e5m2>(float v) { return __nv_fp8_e5m2(v); }
+template <>
 __device__ __forceinline__ int8_t fill_cast<int8_t>(float v) {
   return static_cast<int8_t>(fmaxf(-128.f, fminf(127.f, rintf(v))));
 }
@@ -911,7 +932,7 @@ __global__ void fill_kernel(T* ptr, int64_t count, uint64_t seed, uint32_t strea
       const float u2 = static_cast<float>(static_cast<uint32_t>(bits >> 16) & 0xFFFFFFu) * (1.0f / 16777216.0f);
       v = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2) * scale;
     } else {
-      if (sizeof(T) == 1) v = static_cast<float>(gz::rng_int8(bits));
+      if (std::is_same<T, int8_t>::value) v = static_cast<float>(gz::rng_int8(bits));
       else {
         const int32_t span = 2 * static_cast<int32_t>(scale) + 1;
         v = static_cast<float>(static_cast<int32_t>((bits >> 33) % static_cast<uint64_t>(span)) -
@@ -947,6 +968,12 @@ extern "C" GZ_API gz_status gz_fill(void* ptr, int32_t dtype, int64_t count, uin
       break;
     case GZ_DT_S32:
       fill_kernel<int32_t><<<grid, block, 0, stream>>>((int32_t*)ptr, count, seed, stream_id, dist, scale);
+      break;
+    case GZ_DT_E4M3:
+      fill_kernel<__nv_fp8_e4m3><<<grid, block, 0, stream>>>((__nv_fp8_e4m3*)ptr, count, seed, stream_id, dist, scale);
+      break;
+    case GZ_DT_E5M2:
+      fill_kernel<__nv_fp8_e5m2><<<grid, block, 0, stream>>>((__nv_fp8_e5m2*)ptr, count, seed, stream_id, dist, scale);
       break;
   }
   if (!cuda_ok(cudaGetLastError(), "fill launch")) return GZ_ERR_CUDA;

@@ -258,7 +258,7 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
       : "memory");
 }
 
-enum class Kind : int { F16 = 0, TF32 = 1, I8 = 2 };
+enum class Kind : int { F16 = 0, TF32 = 1, I8 = 2, F8 = 3 };
 
 // D[tmem] (+)= A[smem desc] * B[smem desc]; issued by ONE thread.
 template <Kind KIND, int CTAS>
@@ -277,10 +277,12 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
   if constexpr (CTAS == 1) {
     if constexpr (KIND == Kind::F16) GZ_UMMA("1", "f16");
     else if constexpr (KIND == Kind::TF32) GZ_UMMA("1", "tf32");
+    else if constexpr (KIND == Kind::F8) GZ_UMMA("1", "f8f6f4");
     else GZ_UMMA("1", "i8");
   } else {
     if constexpr (KIND == Kind::F16) GZ_UMMA("2", "f16");
     else if constexpr (KIND == Kind::TF32) GZ_UMMA("2", "tf32");
+    else if constexpr (KIND == Kind::F8) GZ_UMMA("2", "f8f6f4");
     else GZ_UMMA("2", "i8");
   }
 #undef GZ_UMMA

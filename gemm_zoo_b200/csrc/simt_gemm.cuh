@@ -10,8 +10,11 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <type_traits>
 
 namespace gz {
 
@@ -41,6 +44,14 @@ template <>
 __device__ __forceinline__ float simt_to_f<__nv_bfloat16>(__nv_bfloat16 v) {
   return __bfloat162float(v);
 }
+template <>
+__device__ __forceinline__ float simt_to_f<__nv_fp8_e4m3>(__nv_fp8_e4m3 v) {
+  return static_cast<float>(v);
+}
+template <>
+__device__ __forceinline__ float simt_to_f<__nv_fp8_e5m2>(__nv_fp8_e5m2 v) {
+  return static_cast<float>(v);
+}
 template <typename T>
 __device__ __forceinline__ T simt_from_f(float v) {
   return static_cast<T>(v);
@@ -59,7 +70,7 @@ __device__ __forceinline__ __nv_bfloat16 simt_from_f<__nv_bfloat16>(float v) {
 template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
   constexpr int TM = 64, TN = 64, TK = 16;
-  constexpr bool INT = sizeof(TIn) == 1;
+  constexpr bool INT = std::is_same<TIn, int8_t>::value;
   using Acc = typename std::conditional<INT, int32_t, float>::type;
   __shared__ Acc sa[TK][TM + 1];
   __shared__ Acc sb[TK][TN + 1];

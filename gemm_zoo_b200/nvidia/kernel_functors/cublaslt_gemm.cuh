@@ -21,6 +21,7 @@
 #include <cublasLt.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include <cstddef>
@@ -35,7 +36,9 @@ namespace nvidia::kernel_functors {
 struct RowMajor;
 struct ColMajor;
 
-// Runtime-typed core (dtype codes as gz_dtype: 0 f16, 1 bf16, 2 f32, 3 s8, 4 s32).
+// Runtime-typed core (dtype codes as gz_dtype: 0 f16, 1 bf16, 2 f32, 3 s8, 4 s32, 5 e4m3, 6 e5m2).
+// fp8 inputs use fp32 compute (the reference's CUBLAS_COMPUTE_16F for fp8,
+// nvidia/kernel_functors/cublaslt_gemm.cuh:106-109, is not a combination cuBLASLt offers).
 class cublaslt_core {
  public:
   cublaslt_core(int in_type, int out_type, bool a_col_major, bool b_col_major, std::int64_t m,
@@ -120,6 +123,8 @@ class cublaslt_core {
       case 1: return CUDA_R_16BF;
       case 2: return CUDA_R_32F;
       case 3: return CUDA_R_8I;
+      case 5: return CUDA_R_8F_E4M3;
+      case 6: return CUDA_R_8F_E5M2;
       default: return CUDA_R_32I;
     }
   }
@@ -164,6 +169,8 @@ constexpr int lt_dtype_of() {
   else if constexpr (std::is_same_v<T, float>) return 2;
   else if constexpr (std::is_same_v<T, std::int8_t>) return 3;
   else if constexpr (std::is_same_v<T, std::int32_t>) return 4;
+  else if constexpr (std::is_same_v<T, __nv_fp8_e4m3>) return 5;
+  else if constexpr (std::is_same_v<T, __nv_fp8_e5m2>) return 6;
   else static_assert(sizeof(T) == 0, "unsupported element type");
 }
 template <typename T>

@@ -7,7 +7,8 @@
 // so it can be handed to benchmark::benchmark<Kernel, TIn, TOut> unchanged.
 // Differences from the reference functors:
 //   - one template serves every dtype pair: (half,half), (half,float),
-//     (bf16,bf16), (bf16,float), (float,float) = tf32 multiply, (int8,int32);
+//     (bf16,bf16), (bf16,float), (float,float) = tf32 multiply, (int8,int32),
+//     (fp8 e4m3 / e5m2, half | bf16 | float);
 //   - A and B may each be row- or column-major (template tags) and an extended
 //     constructor takes lda/ldb/ldc/ldd; the 4-argument constructor keeps the
 //     reference convention A[m x k] ld=k, B[k x n] ld=n, C/D[m x n] ld=n
@@ -22,6 +23,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include <cstddef>
@@ -44,6 +46,8 @@ constexpr int gz_dtype_of() {
   else if constexpr (std::is_same_v<T, float>) return GZ_DT_F32;
   else if constexpr (std::is_same_v<T, std::int8_t>) return GZ_DT_S8;
   else if constexpr (std::is_same_v<T, std::int32_t>) return GZ_DT_S32;
+  else if constexpr (std::is_same_v<T, __nv_fp8_e4m3>) return GZ_DT_E4M3;
+  else if constexpr (std::is_same_v<T, __nv_fp8_e5m2>) return GZ_DT_E5M2;
   else static_assert(sizeof(T) == 0, "unsupported element type");
 }
 template <typename T>

@@ -8,6 +8,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include <cstddef>
@@ -26,6 +27,8 @@ constexpr int gz_dtype_code() {
   else if constexpr (std::is_same_v<T, float>) return GZ_DT_F32;
   else if constexpr (std::is_same_v<T, std::int8_t>) return GZ_DT_S8;
   else if constexpr (std::is_same_v<T, std::int32_t>) return GZ_DT_S32;
+  else if constexpr (std::is_same_v<T, __nv_fp8_e4m3>) return GZ_DT_E4M3;
+  else if constexpr (std::is_same_v<T, __nv_fp8_e5m2>) return GZ_DT_E5M2;
   else static_assert(sizeof(T) == 0, "unsupported element type");
 }
 

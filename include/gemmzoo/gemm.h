@@ -26,7 +26,7 @@
  *     Reference default: A row-major lda=K, B row-major ldb=N, C/D ld=N
  *     (nvidia/kernels/naive_gemm.cuh:18-20).
  *   - alpha and beta are passed by HOST pointer in the scale type of the
- *     problem: float for f16/bf16/f32 inputs, int32_t for s8 inputs.
+ *     problem: float for f16/bf16/f32/fp8 inputs, int32_t for s8 inputs.
  *   - C is not read when beta == 0 (the rule of nvidia/kernels/generic_gemm.cuh:55).
  *     D may alias C.
  *   - Nothing here exits the process or throws; every entry point returns a
@@ -67,7 +67,12 @@ typedef enum gz_dtype {
   GZ_DT_BF16 = 1,
   GZ_DT_F32 = 2, /* as an input type: fp32 storage, tf32 multiply, fp32 accumulate */
   GZ_DT_S8 = 3,
-  GZ_DT_S32 = 4
+  GZ_DT_S32 = 4,
+  /* 8-bit floating point inputs (outputs: f16, bf16 or f32; fp32 accumulate).  The reference only
+   * declares the intent: nvidia/bench/bench_cublaslt_e4m3.cu:6-21, bench_cublaslt_e5m2.cu and the fp8
+   * branches of nvidia/kernel_functors/cublaslt_gemm.cuh:85-90,106-109; it has no kernel of its own. */
+  GZ_DT_E4M3 = 5, /* 1-4-3, no infinities (CUDA __nv_fp8_e4m3) */
+  GZ_DT_E5M2 = 6  /* 1-5-2 (CUDA __nv_fp8_e5m2) */
 } gz_dtype;
 
 typedef enum gz_layout { GZ_ROW_MAJOR = 0, GZ_COL_MAJOR = 1 } gz_layout;

@@ -17,7 +17,7 @@ from pathlib import Path
 import numpy as np
 
 HERE = Path(__file__).resolve().parent
-DT_F16, DT_BF16, DT_F32, DT_S8, DT_S32 = 0, 1, 2, 3, 4
+DT_F16, DT_BF16, DT_F32, DT_S8, DT_S32, DT_E4M3, DT_E5M2 = 0, 1, 2, 3, 4, 5, 6
 _NP_OF = {DT_F16: np.uint16, DT_BF16: np.uint16, DT_F32: np.float32, DT_S8: np.int8, DT_S32: np.int32}
 
 _lib = None
@@ -66,13 +66,15 @@ def bits_of(t) -> np.ndarray:
     t = t.detach().cpu().contiguous()
     if t.dtype in (torch.float16, torch.bfloat16):
         return t.view(torch.int16).numpy().view(np.uint16)
+    if t.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        return t.view(torch.uint8).numpy()
     return t.numpy()
 
 
 def dtype_code(t) -> int:
     import torch
     return {torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.float32: DT_F32, torch.int8: DT_S8,
-            torch.int32: DT_S32}[t.dtype]
+            torch.int32: DT_S32, torch.float8_e4m3fn: DT_E4M3, torch.float8_e5m2: DT_E5M2}[t.dtype]
 
 
 def _strides(m, n, k, a_col_major, b_col_major, lda, ldb):

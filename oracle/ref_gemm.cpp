@@ -39,7 +39,7 @@
 
 namespace {
 
-enum { DT_F16 = 0, DT_BF16 = 1, DT_F32 = 2, DT_S8 = 3, DT_S32 = 4 };
+enum { DT_F16 = 0, DT_BF16 = 1, DT_F32 = 2, DT_S8 = 3, DT_S32 = 4, DT_E4M3 = 5, DT_E5M2 = 6 };
 
 inline float bf16_to_f32(uint16_t h) {
   uint32_t u = static_cast<uint32_t>(h) << 16;
@@ -56,6 +56,18 @@ inline float f16_to_f32(uint16_t h) {
   else v = std::ldexp(static_cast<float>(man | 0x400u), static_cast<int>(exp) - 25);
   return sign ? -v : v;
 }
+
+// 8-bit floats.  e4m3 (the "fn" flavour CUDA uses): bias 7, no infinities, S.1111.111 is NaN.
+inline float e4m3_to_f32(uint8_t v) {
+  const uint32_t sign = v >> 7, exp = (v >> 3) & 0xFu, man = v & 0x7u;
+  float f;
+  if (exp == 0) f = std::ldexp(static_cast<float>(man), -9);
+  else if (exp == 15 && man == 7) f = NAN;
+  else f = std::ldexp(static_cast<float>(man | 0x8u), static_cast<int>(exp) - 10);
+  return sign ? -f : f;
+}
+// e5m2: bias 15, IEEE-style infinities and NaNs (it is the top byte of an fp16).
+inline float e5m2_to_f32(uint8_t v) { return f16_to_f32(static_cast<uint16_t>(v) << 8); }
 
 // tf32 views of an fp32 value: mode 1 drops the low 13 mantissa bits, mode 2
 // rounds to nearest with ties away from zero (cvt.rna.tf32.f32).
@@ -76,6 +88,8 @@ inline float load_as_f32(const void* p, int dt, int64_t idx) {
     case DT_F32: return static_cast<const float*>(p)[idx];
     case DT_S8: return static_cast<float>(static_cast<const int8_t*>(p)[idx]);
     case DT_S32: return static_cast<float>(static_cast<const int32_t*>(p)[idx]);
+    case DT_E4M3: return e4m3_to_f32(static_cast<const uint8_t*>(p)[idx]);
+    case DT_E5M2: return e5m2_to_f32(static_cast<const uint8_t*>(p)[idx]);
   }
   return 0.f;
 }
@@ -85,16 +99,7 @@ inline double load_as_f64(const void* p, int dt, int64_t idx) {
   return static_cast<double>(load_as_f32(p, dt, idx));
 }
 
-// Pack the rows [i0, i0+rows) of A as fp32 (exact for every supported input
-// type) row-major with k contiguous, and all of B row-major with n contiguous.
-void pack_a(std::vector<float>& out, const void* a, int dt, int64_t i0, int64_t rows, int64_t k,
-            int64_t a_sm, int64_t a_sk, int tf32_mode) {
-  out.resize(static_cast<size_t>(rows) * k);
-  for (int64_t i = 0; i < rows; ++i)
-    for (int64_t kk = 0; kk < k; ++kk)
-      out[i * k + kk] = to_tf32(load_as_f32(a, dt, (i0 + i) * a_sm + kk * a_sk), tf32_mode);
-}
-
+// Pack all of B as fp32 (exact for every supported input type), row-major with n contiguous.
 void pack_b(std::vector<float>& out, const void* b, int dt, int64_t k, int64_t n, int64_t b_sk,
             int64_t b_sn, int tf32_mode) {
   out.resize(static_cast<size_t>(k) * n);

@@ -9,6 +9,7 @@ Error bars (also quoted in DESIGN.md):
                                  |D - R| <= 2^-10 * |R| + 2^-20 * S  (fp16 out)
                                  |D - R| <= 2^-20 * S + 1e-6         (fp32 out)
   tf32 (fp32 in/out), random     |D - R| <= 2^-9 * S
+  fp8 (e4m3/e5m2) inputs, random |D - R| <= u(out) * |R| + 2^-13 * S,  u = 2^-8 bf16, 2^-10 fp16, 0 fp32
 where R is the fp64 oracle value and S = |alpha| * sum_k |a_ik||b_kj| + |beta||c_ij|.
 """
 from __future__ import annotations
@@ -70,6 +71,7 @@ class Case:
 
     def name(self):
         dt = {0: "f16", 1: "bf16", 2: "f32", 3: "s8", 4: "s32"}
+        dt.update({5: "e4m3", 6: "e5m2"})
         return (f"{dt[self.in_type]}->{dt[self.out_type]} {self.m}x{self.n}x{self.k} "
                 f"A{'c' if self.a_col else 'r'}B{'c' if self.b_col else 'r'} a={self.alpha} b={self.beta} "
                 f"cfg={self.config} fl={self.flags} {self.dist} pads={self.pad_a},{self.pad_b},{self.pad_c},{self.pad_d}"
@@ -79,7 +81,8 @@ class Case:
 def torch_dtype(code):
     import torch
     return {gz.DT_F16: torch.float16, gz.DT_BF16: torch.bfloat16, gz.DT_F32: torch.float32,
-            gz.DT_S8: torch.int8, gz.DT_S32: torch.int32}[code]
+            gz.DT_S8: torch.int8, gz.DT_S32: torch.int32, gz.DT_E4M3: torch.float8_e4m3fn,
+            gz.DT_E5M2: torch.float8_e5m2}[code]
 
 
 def _gen(shape, dtype_code, dist, seed, stream, scale):
@@ -93,6 +96,14 @@ def _gen(shape, dtype_code, dist, seed, stream, scale):
         return torch.from_numpy(rng.integers(-1000, 1001, size=shape, dtype=np.int32))
     if dist == "int":
         x = rng.integers(-2, 3, size=shape).astype(np.float32)
+    elif dtype_code in (gz.DT_E4M3, gz.DT_E5M2) and dist == "full":
+        # every finite byte pattern of the 8-bit format, scaled down so that sums stay in range
+        bits = rng.integers(0, 256, size=shape, dtype=np.uint8)
+        t = torch.from_numpy(bits).view(torch_dtype(dtype_code))
+        f = t.float()
+        f = torch.where(torch.isfinite(f), f, torch.zeros_like(f))
+        f = torch.where(f.abs() > 240.0, torch.zeros_like(f), f)
+        return f.to(torch_dtype(dtype_code))
     elif dist == "normal":
         x = (rng.standard_normal(size=shape) * scale).astype(np.float32)
     else:
@@ -176,6 +187,10 @@ def tolerance(case: Case, ref, scale):
     """Per-element allowed |D - R| (float64 array), per the table in the module docstring."""
     if case.in_type == gz.DT_F32:
         return 2.0 ** -9 * scale + 1e-30
+    if case.in_type in (gz.DT_E4M3, gz.DT_E5M2):
+        # fp8 products are exact; the tensor core's fp32 accumulation of them is allowed 2^-13 * S
+        unit = {gz.DT_BF16: 2.0 ** -8, gz.DT_F16: 2.0 ** -10, gz.DT_F32: 0.0}[case.out_type]
+        return unit * np.abs(ref) + 2.0 ** -13 * scale + 1e-7
     if case.out_type == gz.DT_BF16:
         return 2.0 ** -8 * np.abs(ref) + 2.0 ** -20 * scale + 1e-30
     if case.out_type == gz.DT_F16:

@@ -10,6 +10,7 @@ from tests.helpers import Case, check
 pytestmark = pytest.mark.gpu
 
 F16, BF16, F32, S8, S32 = gz.DT_F16, gz.DT_BF16, gz.DT_F32, gz.DT_S8, gz.DT_S32
+E4M3, E5M2 = gz.DT_E4M3, gz.DT_E5M2
 DIRECT, TMA = gz.FLAG_EPILOGUE_DIRECT, gz.FLAG_EPILOGUE_TMA
 TC_CONFIGS = [gz.CFG_1CTA_N256, gz.CFG_1CTA_N128, gz.CFG_1CTA_N64, gz.CFG_2CTA_N256, gz.CFG_2CTA_N128]
 
@@ -180,3 +181,32 @@ def test_tail_wave_is_cut_into_column_strips(config, m, n, in_t, out_t, b_col):
     dist = "full" if in_t == S8 else "int"
     run(Case(in_t, out_t, m, n, 256, b_col=b_col, config=config, dist=dist, alpha=2, beta=1))
     run(Case(in_t, out_t, m - 8, n - 24, 192, b_col=b_col, config=config, dist=dist, alpha=1, beta=0))
+
+
+ALL_CONFIGS = TC_CONFIGS + [gz.CFG_SWAP_M64]
+
+
+@pytest.mark.parametrize("in_t", [E4M3, E5M2])
+@pytest.mark.parametrize("out_t", [F16, BF16, F32])
+@pytest.mark.parametrize("config", ALL_CONFIGS)
+def test_fp8_inputs_exact_integers(in_t, out_t, config):
+    """8-bit float inputs (kind::f8f6f4): small integers are exact in e4m3 and e5m2."""
+    m = 64 if config == gz.CFG_SWAP_M64 else 300
+    run(Case(in_t, out_t, m, 528, 512, b_col=True, config=config, dist="int", alpha=2, beta=-1))
+
+
+@pytest.mark.parametrize("in_t", [E4M3, E5M2])
+@pytest.mark.parametrize("a_col,b_col", [(False, False), (True, False), (True, True), (False, True)])
+def test_fp8_layouts(in_t, a_col, b_col):
+    run(Case(in_t, F32, 384, 512, 384, a_col=a_col, b_col=b_col, dist="int", alpha=1, beta=1))
+    run(Case(in_t, BF16, 256, 384, 256, a_col=a_col, b_col=b_col, config=gz.CFG_2CTA_N256, dist="int"))
+
+
+@pytest.mark.parametrize("in_t", [E4M3, E5M2])
+@pytest.mark.parametrize("out_t", [F16, F32])
+def test_fp8_every_byte_pattern_within_tolerance(in_t, out_t):
+    """Operands drawn from all finite byte patterns of the format (subnormals included)."""
+    r = run(Case(in_t, out_t, 512, 640, 1024, b_col=True, dist="full", alpha=2.0 ** -10, beta=0.5))
+    assert r["mismatches"] == 0
+    r = run(Case(in_t, out_t, 33, 77, 45, dist="full", alpha=2.0 ** -10, beta=0.0, pad_a=1, pad_b=3, pad_d=5))
+    assert r["config"] == gz.CFG_SIMT

@@ -142,3 +142,12 @@ def test_oracle_matches_reference_kernels_golden():
             assert (np.abs(r - _f(d, ot)) <= 2.0 ** -20 * scale + 1e-6).all(), (idx, line)
         checked += 1
     assert checked == len(z["meta"]) >= 8
+
+
+@pytest.mark.parametrize("tdt,code", [(torch.float8_e4m3fn, orc.DT_E4M3), (torch.float8_e5m2, orc.DT_E5M2)])
+def test_fp8_decoding_matches_every_byte_pattern(tdt, code):
+    allb = torch.arange(256, dtype=torch.uint8).view(tdt)
+    vals = allb.float().double().numpy()
+    one = torch.ones(1, 1).to(tdt)
+    r = orc.gemm_f64(code, orc.DT_F32, orc.bits_of(allb.view(256, 1)), orc.bits_of(one), None, 256, 1, 1)[:, 0]
+    assert bool(((r == vals) | (np.isnan(r) & np.isnan(vals))).all())
