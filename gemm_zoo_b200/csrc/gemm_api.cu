@@ -450,6 +450,17 @@ struct gz_plan {
   // device staging for gz_gemm_run_host
   void *ha, *hb, *hc, *hd;
   size_t ha_bytes, hb_bytes, hcd_bytes;
+  // gz_gemm_run_host pipeline: column blocks of B/C/D travel on two copy streams while the
+  // caller's stream computes (PCIe is full duplex, so uploads, GEMMs and downloads overlap).
+  static constexpr int kMaxBlocks = 16;
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  cudaEvent_t ev_start = nullptr, ev_out = nullptr;
+  cudaEvent_t ev_in[kMaxBlocks] = {}, ev_gemm[kMaxBlocks] = {};
+  gz_plan* block_plan = nullptr;  // plan for one full column block
+  gz_plan* tail_plan = nullptr;   // plan for the last, narrower block (if any)
+  int64_t block_cols = 0;
+  int blocks = 0;
+  bool pipe_ready = false;
   std::mutex mu;
 };
 
@@ -715,6 +726,16 @@ GZ_API gz_status gz_gemm_plan_destroy(gz_plan* pl) {
   if (pl->hb) cudaFree(pl->hb);
   if (pl->hc) cudaFree(pl->hc);
   if (pl->hd) cudaFree(pl->hd);
+  if (pl->block_plan) gz_gemm_plan_destroy(pl->block_plan);
+  if (pl->tail_plan) gz_gemm_plan_destroy(pl->tail_plan);
+  if (pl->copy_in) cudaStreamDestroy(pl->copy_in);
+  if (pl->copy_out) cudaStreamDestroy(pl->copy_out);
+  if (pl->ev_start) cudaEventDestroy(pl->ev_start);
+  if (pl->ev_out) cudaEventDestroy(pl->ev_out);
+  for (int i = 0; i < gz_plan::kMaxBlocks; ++i) {
+    if (pl->ev_in[i]) cudaEventDestroy(pl->ev_in[i]);
+    if (pl->ev_gemm[i]) cudaEventDestroy(pl->ev_gemm[i]);
+  }
   delete pl;
   return GZ_OK;
 }
@@ -858,15 +879,106 @@ GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, con
         return GZ_ERR_OUT_OF_MEMORY;
     }
   }
-  if (!cuda_ok(cudaMemcpyAsync(pl->ha, a, a_bytes, cudaMemcpyHostToDevice, stream), "H2D A") ||
-      !cuda_ok(cudaMemcpyAsync(pl->hb, b, b_bytes, cudaMemcpyHostToDevice, stream), "H2D B"))
-    return GZ_ERR_CUDA;
-  if (!beta_zero &&
-      !cuda_ok(cudaMemcpyAsync(pl->hc, c, c_bytes, cudaMemcpyHostToDevice, stream), "H2D C"))
-    return GZ_ERR_CUDA;
-  st = gz_gemm_run(pl, pl->ha, pl->hb, beta_zero ? nullptr : pl->hc, pl->hd, alpha, beta, stream_v);
-  if (st != GZ_OK) return st;
-  if (!cuda_ok(cudaMemcpyAsync(d, pl->hd, d_bytes, cudaMemcpyDeviceToHost, stream), "D2H D") ||
+  // Small problems: one upload, one launch, one download on the caller's stream.
+  const bool pipelined = (a_bytes + b_bytes + d_bytes >= (size_t(32) << 20)) && pr.d.n >= 2048;
+  if (!pipelined) {
+    if (!cuda_ok(cudaMemcpyAsync(pl->ha, a, a_bytes, cudaMemcpyHostToDevice, stream), "H2D A") ||
+        !cuda_ok(cudaMemcpyAsync(pl->hb, b, b_bytes, cudaMemcpyHostToDevice, stream), "H2D B"))
+      return GZ_ERR_CUDA;
+    if (!beta_zero &&
+        !cuda_ok(cudaMemcpyAsync(pl->hc, c, c_bytes, cudaMemcpyHostToDevice, stream), "H2D C"))
+      return GZ_ERR_CUDA;
+    st = gz_gemm_run(pl, pl->ha, pl->hb, beta_zero ? nullptr : pl->hc, pl->hd, alpha, beta, stream_v);
+    if (st != GZ_OK) return st;
+    if (!cuda_ok(cudaMemcpyAsync(d, pl->hd, d_bytes, cudaMemcpyDeviceToHost, stream), "D2H D") ||
+        !cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize"))
+      return GZ_ERR_CUDA;
+    return GZ_OK;
+  }
+
+  // Large problems: A goes up first, then B (and C) in column blocks; block j is multiplied on the
+  // caller's stream as soon as it has landed, and its block of D goes down while later blocks are
+  // still going up.
+  {
+    std::lock_guard<std::mutex> lock(pl->mu);
+    if (!pl->pipe_ready) {
+      int64_t cols = cdiv(cdiv(pr.d.n, 8), 256) * 256;  // about 8 blocks, 256-column granularity
+      if (cols < 256) cols = 256;
+      int blocks = (int)cdiv(pr.d.n, cols);
+      if (blocks > gz_plan::kMaxBlocks) {
+        cols = cdiv(cdiv(pr.d.n, gz_plan::kMaxBlocks), 256) * 256;
+        blocks = (int)cdiv(pr.d.n, cols);
+      }
+      gz_gemm_desc bd = pr.d;
+      bd.flags &= ~GZ_FLAG_TEST_WITHHOLD_ACC_READY;
+      bd.config = GZ_CFG_AUTO;
+      bd.n = cols < pr.d.n ? cols : pr.d.n;
+      if ((st = gz_gemm_plan_create(&pl->block_plan, &bd)) != GZ_OK) return st;
+      const int64_t tail = pr.d.n - (int64_t)(blocks - 1) * cols;
+      if (blocks > 1 && tail != cols) {
+        bd.n = tail;
+        if ((st = gz_gemm_plan_create(&pl->tail_plan, &bd)) != GZ_OK) return st;
+      }
+      bool ok = cuda_ok(cudaStreamCreateWithFlags(&pl->copy_in, cudaStreamNonBlocking), "cudaStreamCreate") &&
+                cuda_ok(cudaStreamCreateWithFlags(&pl->copy_out, cudaStreamNonBlocking), "cudaStreamCreate") &&
+                cuda_ok(cudaEventCreateWithFlags(&pl->ev_start, cudaEventDisableTiming), "cudaEventCreate") &&
+                cuda_ok(cudaEventCreateWithFlags(&pl->ev_out, cudaEventDisableTiming), "cudaEventCreate");
+      for (int i = 0; ok && i < blocks; ++i)
+        ok = cuda_ok(cudaEventCreateWithFlags(&pl->ev_in[i], cudaEventDisableTiming), "cudaEventCreate") &&
+             cuda_ok(cudaEventCreateWithFlags(&pl->ev_gemm[i], cudaEventDisableTiming), "cudaEventCreate");
+      if (!ok) return GZ_ERR_CUDA;
+      pl->block_cols = cols;
+      pl->blocks = blocks;
+      pl->pipe_ready = true;
+    }
+  }
+  const int64_t cols = pl->block_cols;
+  const size_t isz = pr.in_size, osz = pr.out_size;
+  bool ok = cuda_ok(cudaEventRecord(pl->ev_start, stream), "cudaEventRecord") &&
+            cuda_ok(cudaStreamWaitEvent(pl->copy_in, pl->ev_start, 0), "cudaStreamWaitEvent") &&
+            cuda_ok(cudaStreamWaitEvent(pl->copy_out, pl->ev_start, 0), "cudaStreamWaitEvent") &&
+            cuda_ok(cudaMemcpyAsync(pl->ha, a, a_bytes, cudaMemcpyHostToDevice, pl->copy_in), "H2D A");
+  for (int j = 0; ok && j < pl->blocks; ++j) {
+    const int64_t n0 = (int64_t)j * cols;
+    const int64_t nj = (n0 + cols <= pr.d.n) ? cols : pr.d.n - n0;
+    if (!pr.b_mn_major) {  // column-major B: a column block is contiguous
+      const size_t off = (size_t)n0 * pr.d.ldb * isz;
+      ok = cuda_ok(cudaMemcpyAsync(static_cast<char*>(pl->hb) + off, static_cast<const char*>(b) + off,
+                                   (size_t)nj * pr.d.ldb * isz, cudaMemcpyHostToDevice, pl->copy_in), "H2D B block");
+    } else {               // row-major B: k rows of nj columns
+      const size_t off = (size_t)n0 * isz, pitch = (size_t)pr.d.ldb * isz;
+      ok = cuda_ok(cudaMemcpy2DAsync(static_cast<char*>(pl->hb) + off, pitch, static_cast<const char*>(b) + off,
+                                     pitch, (size_t)nj * isz, (size_t)pr.d.k, cudaMemcpyHostToDevice, pl->copy_in),
+                   "H2D B block");
+    }
+    if (ok && !beta_zero) {
+      const size_t off = (size_t)n0 * osz, pitch = (size_t)pr.d.ldc * osz;
+      ok = cuda_ok(cudaMemcpy2DAsync(static_cast<char*>(pl->hc) + off, pitch, static_cast<const char*>(c) + off,
+                                     pitch, (size_t)nj * osz, (size_t)pr.d.m, cudaMemcpyHostToDevice, pl->copy_in),
+                   "H2D C block");
+    }
+    ok = ok && cuda_ok(cudaEventRecord(pl->ev_in[j], pl->copy_in), "cudaEventRecord");
+  }
+  if (!ok) return GZ_ERR_CUDA;
+  for (int j = 0; j < pl->blocks; ++j) {
+    const int64_t n0 = (int64_t)j * cols;
+    const int64_t nj = (n0 + cols <= pr.d.n) ? cols : pr.d.n - n0;
+    gz_plan* sub = (nj == cols || !pl->tail_plan) ? pl->block_plan : pl->tail_plan;
+    const char* bj = static_cast<const char*>(pl->hb) + (pr.b_mn_major ? (size_t)n0 * isz : (size_t)n0 * pr.d.ldb * isz);
+    const char* cj = static_cast<const char*>(pl->hc) + (size_t)n0 * osz;
+    char* dj = static_cast<char*>(pl->hd) + (size_t)n0 * osz;
+    if (!cuda_ok(cudaStreamWaitEvent(stream, pl->ev_in[j], 0), "cudaStreamWaitEvent")) return GZ_ERR_CUDA;
+    st = gz_gemm_run(sub, pl->ha, bj, beta_zero ? nullptr : cj, dj, alpha, beta, stream_v);
+    if (st != GZ_OK) return st;
+    const size_t pitch_h = (size_t)pr.d.ldd * osz;
+    if (!cuda_ok(cudaEventRecord(pl->ev_gemm[j], stream), "cudaEventRecord") ||
+        !cuda_ok(cudaStreamWaitEvent(pl->copy_out, pl->ev_gemm[j], 0), "cudaStreamWaitEvent") ||
+        !cuda_ok(cudaMemcpy2DAsync(static_cast<char*>(d) + (size_t)n0 * osz, pitch_h, dj, pitch_h, (size_t)nj * osz,
+                                   (size_t)pr.d.m, cudaMemcpyDeviceToHost, pl->copy_out), "D2H D block"))
+      return GZ_ERR_CUDA;
+  }
+  if (!cuda_ok(cudaEventRecord(pl->ev_out, pl->copy_out), "cudaEventRecord") ||
+      !cuda_ok(cudaStreamWaitEvent(stream, pl->ev_out, 0), "cudaStreamWaitEvent") ||
       !cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize"))
     return GZ_ERR_CUDA;
   return GZ_OK;

@@ -164,7 +164,10 @@ GZ_API gz_status gz_gemm_run(gz_plan* plan, const void* a, const void* b, const 
 
 /* Same computation with HOST operands: copies A, B (and C when beta != 0) to
  * device staging owned by the plan, runs, copies D back, and synchronises the
- * stream before returning. */
+ * stream before returning.  Large problems are pipelined: B, C and D travel in
+ * column blocks on two internal copy streams while the GEMM of each block runs
+ * on `stream`, so uploads, compute and downloads overlap (give it pinned host
+ * memory; pageable memory works but serialises the copies). */
 GZ_API gz_status gz_gemm_run_host(gz_plan* plan, const void* a, const void* b, const void* c, void* d,
                                   const void* alpha, const void* beta, void* stream);
 
