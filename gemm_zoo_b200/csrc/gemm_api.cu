@@ -162,7 +162,7 @@ bool shape_fits(const Problem& pr, const CfgShape& s) {
 
 // Split-K is implemented by the swapped (skinny) tiles only.  It pays when whole tiles would
 // occupy at most half of the SMs (with more than that streaming, HBM is already saturated) and
-// every CTA still gets a few K blocks.
+// there are enough K blocks to share out (each CTA gets at least four).
 bool wants_split_k(const Problem& pr, const CfgShape& s, int sm_count) {
   if (!s.swap || (pr.d.flags & GZ_FLAG_NO_SPLIT_K)) return false;
   const int64_t k_blocks = cdiv(pr.d.k, 128 / pr.in_size);
@@ -170,7 +170,8 @@ bool wants_split_k(const Problem& pr, const CfgShape& s, int sm_count) {
   const int64_t total = tiles * k_blocks;
   if (total < 2) return false;
   if (pr.d.flags & GZ_FLAG_SPLIT_K) return true;
-  return tiles * 2 <= sm_count && total >= (int64_t)sm_count * 4;
+  // Wide partial tiles are costly to park and add up; left to the caller's explicit request.
+  return s.bn <= 64 && tiles * 2 <= sm_count && total >= 16;
 }
 
 // Tail splitting for whole-tile schedules: if the last wave would fill at most half (a quarter) of
@@ -192,6 +193,20 @@ int tail_parts_for(const Problem& pr, const CfgShape& s, int64_t tiles, int64_t 
   }
   if (parts > 1) *first = tiles - rem;
   return parts;
+}
+
+// CTAs a split-K launch uses: each gets at least four K blocks, and a tile is shared by few enough
+// CTAs that the partial sums its finisher must add stay around 256 KB.
+int64_t split_k_grid(const CfgShape& s, int64_t tiles, int64_t k_blocks, int64_t units) {
+  const int64_t total = tiles * k_blocks;
+  const int64_t slot_bytes = (int64_t)s.bn * 128 * 4;
+  int64_t share = (256 * 1024) / slot_bytes;  // CTAs per tile
+  if (share < 2) share = 2;
+  int64_t grid = cdiv(total, 4);
+  if (grid > tiles * share) grid = tiles * share;
+  if (grid > units) grid = units;
+  if (grid < 1) grid = 1;
+  return grid;
 }
 
 // Pick the tile shape with the least estimated time.  Per 128-byte K block a CTA is held up by
@@ -217,7 +232,11 @@ int choose_config(const Problem& pr, int sm_count) {
     if (issue > per_block) per_block = issue;
     double blocks_per_cta;
     if (wants_split_k(pr, s, sm_count)) {
-      blocks_per_cta = double(cdiv(tiles * k_blocks, units));
+      const int64_t total = tiles * k_blocks;
+      const int64_t ctas = split_k_grid(s, tiles, k_blocks, units);
+      // plus parking one partial tile and, for the finisher, adding the others (64 bytes per cycle)
+      const double share = double(ctas) / double(tiles) + 1.0;
+      blocks_per_cta = double(cdiv(total, ctas)) + share * (s.bn * 128.0 * 4.0 / 64.0) / per_block;
     } else {
       int64_t first;
       const int parts = tail_parts_for(pr, s, tiles, units, &first);
@@ -264,7 +283,7 @@ void fill_info(const Problem& pr, int config, int sm_count, gz_plan_info* info) 
   if (wants_split_k(pr, *s, sm_count)) {
     const int64_t k_blocks = cdiv(pr.d.k, info->tile_k);
     const int64_t total = info->tiles * k_blocks;
-    const int64_t grid = units < total ? units : total;
+    const int64_t grid = split_k_grid(*s, info->tiles, k_blocks, units);
     const int64_t shortest = total / grid;  // K blocks in the shortest range
     const int64_t contrib = (k_blocks - 1) / shortest + 2;
     info->split_k = 1;

@@ -94,7 +94,7 @@ struct GemmParams {
   uint32_t split_k;
   uint32_t max_contrib;          // workspace slots per tile
   unsigned long long total_kb;   // num_tiles * k_blocks
-  float* ws;                     // [num_tiles][max_contrib][128][BN] partial accumulators (fp32 or int32 bits)
+  float* ws;                     // [num_tiles][max_contrib][BN/4][128] float4 partial accumulators (fp32 or int32 bits)
   int* counters;                 // [num_tiles], zero between launches
   // Tuning switches (see TUNE_* below).
   uint32_t tune;
@@ -701,9 +701,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           break;
         }
         const long long e0 = prof ? clock64() : 0;
-        // Workspace layout: [tile][slot][128 accumulator lanes][BN columns]; a thread owns one
-        // lane's BN consecutive floats and moves them 16 bytes at a time.
-        const size_t lane_off = static_cast<size_t>(quad * 32u + lane) * BN;
+        // Workspace layout: [tile][slot][BN / 4][128 accumulator lanes] of float4 (4 consecutive
+        // columns of one lane), so that the 32 lanes of a warp always touch 512 contiguous bytes.
+        const size_t lane_off = static_cast<size_t>(quad * 32u + lane);
+        constexpr size_t SLOT_F4 = static_cast<size_t>(BN) * 128u / 4u;  // float4 per slot
         if (partial) {
           // This CTA holds only part of the tile's K range.  Park the partial accumulator in this
           // CTA's workspace slot; the CTA that arrives last adds the slots in K order and writes
@@ -713,8 +714,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           const uint32_t last = detail::split_owner(tile_u0 + k_blocks - 1u, p.total_kb, num_clusters);
           contributors = last - first + 1u;
           my_slot = cluster - first;
-          float4* slot = reinterpret_cast<float4*>(
-              p.ws + (static_cast<size_t>(t) * p.max_contrib + my_slot) * (BN * 128u) + lane_off);
+          float4* slot = reinterpret_cast<float4*>(p.ws) +
+                         (static_cast<size_t>(t) * p.max_contrib + my_slot) * SLOT_F4 + lane_off;
 #pragma unroll
           for (int sl = 0; sl < BN / 16; ++sl) {
             uint32_t v[16];
@@ -722,8 +723,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             ptx::tmem_wait_ld();
 #pragma unroll
             for (int q = 0; q < 4; ++q)
-              slot[sl * 4 + q] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
-                                             __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+              slot[(sl * 4 + q) * 128] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                                     __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
           }
           __threadfence();
           ptx::named_barrier_sync(1, 128);  // all four epilogue warps have parked their rows
@@ -750,26 +751,38 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               ptx::tmem_ld_32x16(taddr + sl * 16u, v);
               ptx::tmem_wait_ld();
             } else {
-              const float4* s0 = reinterpret_cast<const float4*>(
-                  p.ws + static_cast<size_t>(t) * p.max_contrib * (BN * 128u) + lane_off) + sl * 4;
+              // Slots are added in K order, four at a time so that their loads overlap.
+              const float4* s0 = reinterpret_cast<const float4*>(p.ws) +
+                                 static_cast<size_t>(t) * p.max_contrib * SLOT_F4 + lane_off + (sl * 4) * 128;
               float4 sum[4];
+              for (uint32_t c0 = 0; c0 < contributors; c0 += 4u) {
+                float4 x[4][4];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) sum[q] = __ldcg(s0 + q);
-              for (uint32_t c = 1; c < contributors; ++c) {
-                const float4* sc = s0 + static_cast<size_t>(c) * (BN * 128u / 4u);
+                for (int cc = 0; cc < 4; ++cc) {
+                  const bool have = c0 + cc < contributors;
+                  const float4* sc = s0 + static_cast<size_t>(c0 + cc) * SLOT_F4;
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  const float4 x = __ldcg(sc + q);
-                  if constexpr (detail::OutTraits<TOut>::INT) {
-                    sum[q].x = __uint_as_float(__float_as_uint(sum[q].x) + __float_as_uint(x.x));
-                    sum[q].y = __uint_as_float(__float_as_uint(sum[q].y) + __float_as_uint(x.y));
-                    sum[q].z = __uint_as_float(__float_as_uint(sum[q].z) + __float_as_uint(x.z));
-                    sum[q].w = __uint_as_float(__float_as_uint(sum[q].w) + __float_as_uint(x.w));
-                  } else {
-                    sum[q].x += x.x;
-                    sum[q].y += x.y;
-                    sum[q].z += x.z;
-                    sum[q].w += x.w;
+                  for (int q = 0; q < 4; ++q)
+                    x[cc][q] = have ? __ldcg(sc + q * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                  if (c0 + cc >= contributors) break;
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    if (c0 + cc == 0u) {
+                      sum[q] = x[cc][q];
+                    } else if constexpr (detail::OutTraits<TOut>::INT) {
+                      sum[q].x = __uint_as_float(__float_as_uint(sum[q].x) + __float_as_uint(x[cc][q].x));
+                      sum[q].y = __uint_as_float(__float_as_uint(sum[q].y) + __float_as_uint(x[cc][q].y));
+                      sum[q].z = __uint_as_float(__float_as_uint(sum[q].z) + __float_as_uint(x[cc][q].z));
+                      sum[q].w = __uint_as_float(__float_as_uint(sum[q].w) + __float_as_uint(x[cc][q].w));
+                    } else {
+                      sum[q].x += x[cc][q].x;
+                      sum[q].y += x[cc][q].y;
+                      sum[q].z += x[cc][q].z;
+                      sum[q].w += x[cc][q].w;
+                    }
                   }
                 }
               }
