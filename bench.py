@@ -23,6 +23,7 @@ Keys beyond the base contract:
   e2e           same metric through gz_gemm_run_host with pinned HOST operands: H2D of A
                 and B and D2H of D inside the timed region
   cublaslt      cuBLASLt on the same operands in the same process, interleaved
+  sustained     (--sustain S) seconds-long loops of own kernel and cuBLASLt: TFLOP/s, SM clock, watts
   other_dtypes  fp16 / tf32 / s8 / fp8 at 8192^3 and the bf16 4096^3 beta=0.5 config (own | cuBLASLt)
 """
 from __future__ import annotations
@@ -189,6 +190,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip cuBLASLt / other dtypes / CPU baseline")
+    ap.add_argument("--sustain", type=float, default=0.0,
+                    help="also run own kernel and cuBLASLt back to back for this many seconds each and "
+                         "report throughput, SM clock and board power under the power cap")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "own" else args.warmup
 
@@ -305,6 +309,9 @@ def main():
         "clocks": clocks,
     }
 
+    if rank == 0 and world == 1 and args.sustain > 0:
+        line["sustained"] = sustained_compare(gz, torch, dev, stream, A, B, D, gemm, flops, args.sustain,
+                                              physical_gpu_index(local_rank))
     if rank == 0 and world == 1 and not args.no_extras:
         try:
             line["cublaslt"] = compare_cublaslt(gz, torch, dev, stream, A, B, D, gemm, flops)
@@ -346,6 +353,53 @@ def _time_interleaved(torch, stream, fns, sets, reps=20, warm=3):
     for ts in times:
         v = sorted(s.elapsed_time(e) for s, e in ts)
         out.append(v[len(v) // 2])
+    return out
+
+
+def sustained_compare(gz, torch, dev, stream, A, B, D, gemm, flops, seconds, nvml_index):
+    """Seconds-long back-to-back loops (the power-capped regime): TFLOP/s, median SM clock and board
+    power over the second half of each loop, own kernel then cuBLASLt, twice."""
+    import pynvml
+    from gemm_zoo_b200.cublaslt import CublasLtGemm
+    pynvml.nvmlInit()
+    h = pynvml.nvmlDeviceGetHandleByIndex(nvml_index)
+    lt = CublasLtGemm(M, N, K, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR)
+
+    def loop(fn):
+        samples, stop = [], threading.Event()
+
+        def sample():
+            while not stop.is_set():
+                samples.append((pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM),
+                                pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0))
+                time.sleep(0.02)
+        th = threading.Thread(target=sample, daemon=True)
+        th.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n, t0 = 0, time.time()
+        e0.record(stream)
+        while time.time() - t0 < seconds:
+            for _ in range(100):
+                fn(n % len(A))
+                n += 1
+            torch.cuda.synchronize()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        stop.set()
+        th.join()
+        ms = e0.elapsed_time(e1) / n
+        half = samples[len(samples) // 2:] or [(0, 0.0)]
+        clk = sorted(x[0] for x in half)[len(half) // 2]
+        pw = sorted(x[1] for x in half)[len(half) // 2]
+        return {"tflops": flops / ms / 1e9, "ms": ms, "sm_mhz": clk, "watts": pw}
+
+    out = {"seconds_each": seconds, "own": [], "cublaslt": []}
+    for _ in range(2):
+        out["own"].append(loop(lambda i: gemm(A[i], B[i], None, D, 1.0, 0.0, stream)))
+        time.sleep(1.0)
+        out["cublaslt"].append(loop(lambda i: lt(A[i], B[i], None, D, 1.0, 0.0, stream)))
+        time.sleep(1.0)
+    lt.destroy()
     return out
 
 
