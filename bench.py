@@ -130,8 +130,9 @@ def cpu_reference_tflops(rows, threads=None):
     """Time the CPU oracle on `rows` rows of the bench workload; returns (TFLOP/s, seconds, cores)."""
     import numpy as np
     from oracle import cpu_oracle as orc
-    if threads:
-        orc.lib().oracle_set_threads(threads)
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its ranks; the baseline is
+    # defined on all cores this process may run on, so set the count explicitly.
+    orc.lib().oracle_set_threads(threads or len(os.sched_getaffinity(0)))
     if "b" not in _CPU_DATA:
         rng = np.random.default_rng(1)
         # bf16 bit patterns of N(0,1) and N(0,1)/sqrt(K): top 16 bits of the fp32 values.
