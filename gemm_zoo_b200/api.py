@@ -14,6 +14,7 @@ DT_F16, DT_BF16, DT_F32, DT_S8, DT_S32, DT_E4M3, DT_E5M2 = 0, 1, 2, 3, 4, 5, 6
 ROW_MAJOR, COL_MAJOR = 0, 1
 CFG_AUTO, CFG_1CTA_N256, CFG_1CTA_N128, CFG_1CTA_N64, CFG_2CTA_N256, CFG_2CTA_N128, CFG_SIMT = 0, 1, 2, 3, 4, 5, 15
 CFG_SWAP_M16, CFG_SWAP_M32, CFG_SWAP_M64, CFG_SWAP_M128 = 6, 7, 8, 9
+CFG_2CTA_M512_N256 = 10
 FLAG_EPILOGUE_DIRECT, FLAG_EPILOGUE_TMA, FLAG_TEST_WITHHOLD_ACC_READY = 0x1, 0x2, 0x80000000
 FLAG_NO_SPLIT_K, FLAG_SPLIT_K = 0x4, 0x8
 

@@ -82,13 +82,15 @@ bool pair_supported(int in, int out) {
 struct CfgShape {
   int config, ctas, bn, stages;
   bool swap;  // operand roles exchanged: the 128-row side walks N, the bn side walks M
+  int mb;     // 128-row blocks of the wide operand per CTA
+  int tile_wide() const { return 128 * ctas * mb; }  // tile extent along the 128-row side
 };
 const CfgShape kShapes[] = {
-    {GZ_CFG_2CTA_N256, 2, 256, 6, false}, {GZ_CFG_1CTA_N256, 1, 256, 4, false},
-    {GZ_CFG_2CTA_N128, 2, 128, 8, false}, {GZ_CFG_1CTA_N128, 1, 128, 6, false},
-    {GZ_CFG_1CTA_N64, 1, 64, 8, false},   {GZ_CFG_SWAP_M16, 1, 16, 12, true},
-    {GZ_CFG_SWAP_M32, 1, 32, 11, true},   {GZ_CFG_SWAP_M64, 1, 64, 9, true},
-    {GZ_CFG_SWAP_M128, 1, 128, 6, true},
+    {GZ_CFG_2CTA_N256, 2, 256, 6, false, 1}, {GZ_CFG_1CTA_N256, 1, 256, 4, false, 1},
+    {GZ_CFG_2CTA_N128, 2, 128, 8, false, 1}, {GZ_CFG_1CTA_N128, 1, 128, 6, false, 1},
+    {GZ_CFG_1CTA_N64, 1, 64, 8, false, 1},   {GZ_CFG_SWAP_M16, 1, 16, 12, true, 1},
+    {GZ_CFG_SWAP_M32, 1, 32, 11, true, 1},   {GZ_CFG_SWAP_M64, 1, 64, 9, true, 1},
+    {GZ_CFG_SWAP_M128, 1, 128, 6, true, 1},  {GZ_CFG_2CTA_M512_N256, 2, 256, 4, false, 2},
 };
 const CfgShape* shape_of(int config) {
   for (const auto& s : kShapes)
@@ -189,6 +191,8 @@ int tail_parts_for(const Problem& pr, const CfgShape& s, int64_t tiles, int64_t 
     if (strip < 64 || rem * f > units) break;
     if (pr.b_mn_major && (strip / s.ctas) % chunk != 0) break;  // N-contiguous B is fetched in 128-byte chunks
     if ((strip / s.ctas) % 8 != 0) break;
+    // two-row-block tiles: each epilogue warp stores whole 128-byte boxes of its half of the strip
+    if (s.mb == 2 && (strip / 2) % (128 / pr.out_size) != 0) break;
     parts = f;
   }
   if (parts > 1) *first = tiles - rem;
@@ -212,8 +216,12 @@ int64_t split_k_grid(const CfgShape& s, int64_t tiles, int64_t k_blocks, int64_t
 // Pick the tile shape with the least estimated time.  Per 128-byte K block a CTA is held up by
 // the slowest of: the MMAs (a 128 x bn x 32-byte MMA takes bn/2 cycles, four per block), the
 // L2 -> shared-memory fill of its stage (about 64 bytes per cycle per SM), and the issue cost of
-// the block (about 250 cycles).  Whole tiles are dealt to the SMs in waves; with split-K the K
-// blocks of all tiles are spread evenly.
+// the block (about 250 cycles).  On top of that, every byte moved costs power, and a large GEMM
+// runs at the part's power limit, where power is paid for in clock frequency: 35 % of the fill
+// time is added for it (fitted to measurements of the 256- and 512-row tiles at 8192^3 and
+// 16384^3).  Tiles with two row blocks per CTA expose part of their epilogue once per tile.
+// Whole tiles are dealt to the SMs in waves; with split-K the K blocks of all tiles are spread
+// evenly.
 int choose_config(const Problem& pr, int sm_count) {
   if (!pr.tma_ld_ok) return GZ_CFG_SIMT;
   double best = 0;
@@ -222,14 +230,19 @@ int choose_config(const Problem& pr, int sm_count) {
   for (const auto& s : kShapes) {
     if (!shape_fits(pr, s)) continue;
     const int64_t wide = s.swap ? pr.d.n : pr.d.m, narrow = s.swap ? pr.d.m : pr.d.n;
-    const int64_t tiles = cdiv(wide, 128 * s.ctas) * cdiv(narrow, s.bn);
+    const int64_t tiles = cdiv(wide, s.tile_wide()) * cdiv(narrow, s.bn);
     const int64_t units = sm_count / s.ctas;
     if (units <= 0) continue;
-    const double mma = 4.0 * (s.bn / 2.0);
-    const double fill = (128.0 + double(s.bn) / s.ctas) * 128.0 / 64.0;
+    const double mma = 4.0 * (s.bn / 2.0) * s.mb;
+    const double fill = (128.0 * s.mb + double(s.bn) / s.ctas) * 128.0 / 64.0;
     const double issue = 250.0;
     double per_block = mma > fill ? mma : fill;
     if (issue > per_block) per_block = issue;
+    per_block += 0.35 * fill;
+    // Clocks per tile during which the tensor pipe waits for the epilogue: only the accumulator
+    // hand-over when a warp's share of both accumulators fits its registers (16-bit outputs),
+    // most of the output stores otherwise.
+    const double per_tile = s.mb == 2 ? (pr.out_size == 2 ? 3500.0 : 12000.0) : 0.0;
     double blocks_per_cta;
     if (wants_split_k(pr, s, sm_count)) {
       const int64_t total = tiles * k_blocks;
@@ -241,7 +254,7 @@ int choose_config(const Problem& pr, int sm_count) {
       int64_t first;
       const int parts = tail_parts_for(pr, s, tiles, units, &first);
       const double waves = parts > 1 ? double(first / units) + 1.0 / parts : double(cdiv(tiles, units));
-      blocks_per_cta = waves * double(k_blocks);
+      blocks_per_cta = waves * (double(k_blocks) + per_tile / per_block);
     }
     const double cost = blocks_per_cta * per_block;
     if (best == 0 || cost < best) {
@@ -272,7 +285,7 @@ void fill_info(const Problem& pr, int config, int sm_count, gz_plan_info* info) 
     return;
   }
   const CfgShape* s = shape_of(config);
-  info->tile_m = s->swap ? s->bn : 128 * s->ctas;
+  info->tile_m = s->swap ? s->bn : s->tile_wide();
   info->tile_n = s->swap ? 128 : s->bn;
   info->tile_k = 128 / pr.in_size;
   info->stages = s->stages;
@@ -280,6 +293,13 @@ void fill_info(const Problem& pr, int config, int sm_count, gz_plan_info* info) 
   info->tiles = cdiv(pr.d.m, info->tile_m) * cdiv(pr.d.n, info->tile_n);
   const int64_t units = sm_count / s->ctas;
   info->grid = (int32_t)((info->tiles < units ? info->tiles : units) * s->ctas);
+  // Mirrors GemmCfg::SMEM_BYTES: alignment slack, the operand ring, epilogue staging, barriers.
+  const int staging = s->swap ? 0 : (s->mb == 2 ? 8 * 4096 : 4 * 2 * 4096);
+  info->smem_bytes = 1024 + s->stages * (128 * s->mb * 128 + (s->bn / s->ctas) * 128) + staging + 256;
+  // Output rows go through shared memory and TMA stores when D's row pitch allows it; the swapped
+  // (skinny) tiles hold the transposed tile and always store straight from registers.
+  const bool d_tma_ok = (pr.d.ldd * pr.out_size) % 16 == 0;
+  info->epilogue_tma = (!s->swap && d_tma_ok && !(pr.d.flags & GZ_FLAG_EPILOGUE_DIRECT)) ? 1 : 0;
   if (wants_split_k(pr, *s, sm_count)) {
     const int64_t k_blocks = cdiv(pr.d.k, info->tile_k);
     const int64_t total = info->tiles * k_blocks;
@@ -376,6 +396,10 @@ KernelEntry entry_for_shape(int config) {
     case GZ_CFG_SWAP_M128: {
       using C = gz::GemmCfg<KIND, TOut, 128, 1, 6, true>;
       return make_entry<C, false>();
+    }
+    case GZ_CFG_2CTA_M512_N256: {
+      using C = gz::GemmCfg<KIND, TOut, 256, 2, 4, false, 2>;
+      return make_entry<C, WITH_PROF>();
     }
   }
   return {nullptr, nullptr, nullptr, nullptr};
@@ -675,9 +699,9 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
     }
     gz::GemmParams& p = pl->base;
     // Operand "a" of the kernel is whatever rides the 128-row side of the MMA.
-    build_operand(&p.a, s.swap ? pr.b_mn_major : pr.a_mn_major, 128, pr.in_size);
+    build_operand(&p.a, s.swap ? pr.b_mn_major : pr.a_mn_major, 128 * s.mb, pr.in_size);
     build_operand(&p.b, s.swap ? pr.a_mn_major : pr.b_mn_major, s.bn / s.ctas, pr.in_size);
-    const uint32_t tile_m = 128u * s.ctas;
+    const uint32_t tile_m = (uint32_t)s.tile_wide();
     const int64_t wide = s.swap ? pr.d.n : pr.d.m, narrow = s.swap ? pr.d.m : pr.d.n;
     p.grid.tiles_m = (uint32_t)cdiv(wide, tile_m);
     p.grid.tiles_n = (uint32_t)cdiv(narrow, s.bn);

@@ -16,14 +16,26 @@
 //               a tile) issues tcgen05.mma from shared-memory descriptors into
 //               one of two TMEM accumulators and commits each stage back to its
 //               "empty" mbarrier.
-//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (each warp owns
+//   warps 2..5  (and 7..10 when MB == 2)
+//               epilogue: tcgen05.ld the finished accumulator (each warp owns
 //               the 32 TMEM lanes of its warp_id % 4 quadrant), apply
 //               alpha/beta in fp32 (int32 for s8), cast, and either stage rows
 //               in swizzled shared memory for a TMA store or store directly.
 //
-// The second accumulator lets the epilogue of tile i run under the main loop
-// of tile i+1.  No cluster-multicast load is used anywhere: with CTAS == 2 each
-// CTA of the pair loads its own 128 rows of A and its own half of the B tile.
+// With one 128-row block of A per CTA (MB == 1) the second accumulator lets the
+// epilogue of tile i run under the main loop of tile i+1.  With two blocks per
+// CTA (MB == 2: a CTA pair covers 512 x 256 outputs) the two accumulators are
+// the two row blocks of one tile: every B stage feeds twice as many MMAs, so a
+// quarter less data moves from L2 to shared memory per flop.  That pays once the
+// part runs at its power limit, where data movement is paid for in clock
+// frequency.  The price is that the tensor pipe idles from the end of a tile
+// until accumulator 0 is free again, so that hand-over is kept short: eight
+// epilogue warps (two per TMEM lane quadrant, half of the columns each) copy
+// their share to registers and give the accumulator back before storing
+// anything, and the MMA warp starts the next tile with row block 0 alone on
+// the first stages while accumulator 1 is still being copied.
+// No cluster-multicast load is used anywhere: with CTAS == 2 each CTA of the
+// pair loads its own rows of A and its own half of the B tile.
 //
 // Every wait on an mbarrier is bounded (Params::wait_limit_ns).  When a wait
 // expires the waiter records a code in Params::status, raises a CTA-wide abort
@@ -105,7 +117,9 @@ struct GemmParams {
   //  [6] epilogue warp 2: total clocks                 [7] MMA: elapsed nanoseconds (globaltimer)
   //  [8] A producer: clocks issuing copies               [9] MMA: clocks issuing MMAs and commits
   //  [10] B producer: clocks waiting for a free stage   [11] B producer: clocks issuing copies
-  //  [12] epilogue warp 2: clocks parking split-K partial sums
+  //  [12] epilogue warp 2: clocks parking split-K partial sums (two-row-block tiles: clocks copying
+  //       accumulators to registers)
+  //  [13] MMA: clocks waiting for the second accumulator of a two-row-block tile (part of [3])
   // Only kernels instantiated with PROF = true write them.
   unsigned long long* prof;
 };
@@ -120,7 +134,7 @@ enum : uint32_t {
 // skinny problems (M <= 128), where a 128-row A tile would be mostly padding: every byte a stage
 // loads is then a useful byte of B, which is what such HBM-bound shapes need.  The accumulator
 // holds the transpose of the output tile; the epilogue stores it straight to global memory.
-template <ptx::Kind KIND_, typename TOut_, int BN_, int CTAS_, int STAGES_, bool SWAP_ = false>
+template <ptx::Kind KIND_, typename TOut_, int BN_, int CTAS_, int STAGES_, bool SWAP_ = false, int MB_ = 1>
 struct GemmCfg {
   static constexpr ptx::Kind KIND = KIND_;
   static constexpr bool SWAP = SWAP_;
@@ -128,19 +142,23 @@ struct GemmCfg {
   static constexpr int BN = BN_;        // tile columns (= MMA N)
   static constexpr int CTAS = CTAS_;    // CTAs sharing one tile (1 or 2)
   static constexpr int STAGES = STAGES_;
-  static constexpr int BM = 128;                 // tile rows per CTA
+  static constexpr int MB = MB_;                 // 128-row blocks of A per CTA (1 or 2)
+  static constexpr int BM = 128 * MB;            // tile rows per CTA
   static constexpr int BN_CTA = BN / CTAS;       // B rows (tile columns) each CTA loads
-  static constexpr int A_BYTES = BM * 128;       // one stage of A: 128 rows x 128 bytes
+  static constexpr int A_BYTES = BM * 128;       // one stage of A: BM rows x 128 bytes
   static constexpr int B_BYTES = BN_CTA * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGING_WARP_BYTES = SWAP ? 0 : 2 * 4096;  // two 32-row x 128-byte boxes per warp
-  static constexpr int STAGING_BYTES = 4 * STAGING_WARP_BYTES;
+  static constexpr int EPI_WARPS = MB == 2 ? 8 : 4;
+  // 32-row x 128-byte boxes per epilogue warp: two, or one where eight warps share the space
+  static constexpr int STAGING_WARP_BYTES = SWAP ? 0 : (MB == 2 ? 4096 : 2 * 4096);
+  static constexpr int STAGING_BYTES = EPI_WARPS * STAGING_WARP_BYTES;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int TMEM_COLS = 2 * BN;  // two accumulators
-  static constexpr int THREADS = 224;  // 2 producer warps, 1 MMA warp, 4 epilogue warps
+  static constexpr int TMEM_COLS = 2 * BN;  // two accumulators (MB == 2: one per row block)
+  static constexpr int THREADS = 96 + 32 * EPI_WARPS;  // 2 producer warps, 1 MMA warp, 4 or 8 epilogue warps
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "tile N");
   static_assert(!SWAP || (CTAS == 1 && BN <= 128), "swapped tiles are single-CTA and narrow");
+  static_assert(MB == 1 || (MB == 2 && !SWAP), "one or two row blocks per CTA");
   static_assert(TMEM_COLS == 32 || TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
                 "TMEM allocation must be a power of two");
   static_assert(8 * (2 * STAGES + 5) + 12 <= BAR_BYTES, "barrier area");
@@ -287,6 +305,18 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// The two 16-bit values of one 32-bit word (low = first) as fp32.
+template <typename TOut>
+__device__ __forceinline__ float2 unpack2(uint32_t w);
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+
 // alpha * acc + beta * c for one 32-column slice of one row.
 //   v[32]     in:  raw accumulator words;  out: packed output words (32 * sizeof(TOut) / 4 used)
 //   crow      pointer to C(row, col0) (only dereferenced when beta != 0 and row_ok)
@@ -397,6 +427,68 @@ __device__ __forceinline__ void store_direct(const uint32_t (&v)[32], TOut* drow
   }
 }
 
+
+// alpha * acc (+ beta * c) for one full 32-column slice of one row, in place and without a second
+// register array: on return x[0 .. 32 * sizeof(TOut) / 4) holds the packed outputs.  `crow` points
+// at C(row, col0), 16-byte aligned; it is read only when HAS_BETA.
+template <typename TOut, bool HAS_BETA>
+__device__ __forceinline__ void scale_slice_in_place(uint32_t (&x)[32], const GemmParams& p, const TOut* crow) {
+  using Tr = OutTraits<TOut>;
+  const uint4* c4 = reinterpret_cast<const uint4*>(crow);
+  if constexpr (Tr::INT) {
+    const uint32_t alpha = static_cast<uint32_t>(p.alpha_i);
+    const uint32_t beta = static_cast<uint32_t>(p.beta_i);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      uint4 cv = make_uint4(0u, 0u, 0u, 0u);
+      if constexpr (HAS_BETA) cv = c4[q];
+      x[4 * q + 0] = alpha * x[4 * q + 0] + beta * cv.x;
+      x[4 * q + 1] = alpha * x[4 * q + 1] + beta * cv.y;
+      x[4 * q + 2] = alpha * x[4 * q + 2] + beta * cv.z;
+      x[4 * q + 3] = alpha * x[4 * q + 3] + beta * cv.w;
+    }
+  } else if constexpr (sizeof(TOut) == 4) {
+    const float alpha = p.alpha_f, beta = p.beta_f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      float f0 = alpha * __uint_as_float(x[4 * q + 0]), f1 = alpha * __uint_as_float(x[4 * q + 1]);
+      float f2 = alpha * __uint_as_float(x[4 * q + 2]), f3 = alpha * __uint_as_float(x[4 * q + 3]);
+      if constexpr (HAS_BETA) {
+        const uint4 cv = c4[q];
+        f0 = fmaf(beta, __uint_as_float(cv.x), f0);
+        f1 = fmaf(beta, __uint_as_float(cv.y), f1);
+        f2 = fmaf(beta, __uint_as_float(cv.z), f2);
+        f3 = fmaf(beta, __uint_as_float(cv.w), f3);
+      }
+      x[4 * q + 0] = __float_as_uint(f0);
+      x[4 * q + 1] = __float_as_uint(f1);
+      x[4 * q + 2] = __float_as_uint(f2);
+      x[4 * q + 3] = __float_as_uint(f3);
+    }
+  } else {
+    // Eight inputs (words 8q .. 8q+7) become four packed words (4q .. 4q+3): every word is read
+    // before the slot it shares is written.
+    const float alpha = p.alpha_f, beta = p.beta_f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint4 cv = make_uint4(0u, 0u, 0u, 0u);
+      if constexpr (HAS_BETA) cv = c4[q];
+      const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float lo = alpha * __uint_as_float(x[8 * q + 2 * e]);
+        float hi = alpha * __uint_as_float(x[8 * q + 2 * e + 1]);
+        if constexpr (HAS_BETA) {
+          const float2 cf = unpack2<TOut>(cw[e]);
+          lo = fmaf(beta, cf.x, lo);
+          hi = fmaf(beta, cf.y, hi);
+        }
+        x[4 * q + e] = pack2<TOut>(lo, hi);
+      }
+    }
+  }
+}
+
 }  // namespace detail
 
 template <class Cfg, bool PROF = false>
@@ -441,7 +533,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
     if (lane < 2u) {
       ptx::mbar_init(tmem_full_bar(lane), 1);
-      ptx::mbar_init(tmem_empty_bar(lane), 128 * CTAS);
+      ptx::mbar_init(tmem_empty_bar(lane), Cfg::EPI_WARPS * CTAS);  // one arrival per epilogue warp
     }
     if (lane == 2u) {
       ptx::mbar_init(drain_bar, 1);
@@ -494,7 +586,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       uint32_t tm, tn;
       tile_coords(p.grid, t, tm, tn);
       const int32_t row0 = is_b ? static_cast<int32_t>(tn * BN + work.col_off + rank * (work.cols / CTAS))
-                                : static_cast<int32_t>(tm * (128u * CTAS) + rank * 128u);
+                                : static_cast<int32_t>(tm * (Cfg::BM * CTAS) + rank * Cfg::BM);
       for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
         const long long w0 = PROF ? clock64() : 0;
         const bool got = detail::wait(empty_bar(stage), phase ^ 1u, ab, WAIT_PRODUCER_EMPTY, t, kb);
@@ -565,7 +657,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       bool issued = false;
-      long long prof_full = 0, prof_tmem = 0, prof_issue = 0;
+      long long prof_full = 0, prof_tmem = 0, prof_tmem1 = 0, prof_issue = 0;
       const long long prof_t0 = PROF ? clock64() : 0;
       const uint64_t prof_ns0 = PROF ? ptx::globaltimer_ns() : 0;
       const bool mcast = (p.tune & TUNE_COMMIT_MULTICAST) != 0u;
@@ -578,7 +670,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       uint32_t t = 0, kb_lo = 0, kb_hi = 0;
       while (ok && work.next(t, kb_lo, kb_hi)) {
         const long long w0 = PROF ? clock64() : 0;
-        const bool got0 = detail::wait<CTAS == 2>(tmem_empty_bar(acc), acc_phase ^ 1u, ab,
+        const bool got0 = detail::wait(tmem_empty_bar(acc), acc_phase ^ 1u, ab,
                                                   WAIT_MMA_TMEM_EMPTY, t, 0);
         ok = __all_sync(0xFFFFFFFFu, got0);
         if (!ok) break;
@@ -586,7 +678,82 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         const uint32_t idesc_cur = (work.cols == static_cast<uint32_t>(BN)) ? idesc : p.idesc_tail;
-        for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
+        // One row block's four MMAs on stage `st` (128 bytes of K per stage, 32 bytes per MMA).
+        auto issue_block = [&](uint32_t mb, uint32_t kb, uint32_t st) {
+          const uint32_t a_lo = a_lo0 + st * (Cfg::STAGE_BYTES >> 4) + mb * ((128u * 128u) >> 4);
+          const uint32_t b_lo = b_lo0 + st * (Cfg::STAGE_BYTES >> 4);
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            const uint64_t ad = (static_cast<uint64_t>(a_hi) << 32) | (a_lo + j * a_step);
+            const uint64_t bd = (static_cast<uint64_t>(b_hi) << 32) | (b_lo + j * b_step);
+            ptx::umma<Cfg::KIND, CTAS>(d_tmem + mb * BN, ad, bd, idesc_cur, (kb != kb_lo || j != 0u) ? 1u : 0u);
+          }
+        };
+        // Release stage `st` to the producer(s) once the MMAs issued so far have read it.
+        auto release_stage = [&](uint32_t st) {
+          if constexpr (CTAS == 2) {
+            if (mcast) {
+              ptx::tc_commit_pair(empty_bar(st));
+            } else {
+              ptx::tc_commit<CTAS>(empty_bar(st));
+              ptx::tc_commit<CTAS>(ptx::mapa(empty_bar(st), 1));
+            }
+          } else {
+            ptx::tc_commit<CTAS>(empty_bar(st));
+          }
+        };
+        uint32_t kb = kb_lo;
+        if constexpr (Cfg::MB == 2) {
+          // The epilogue frees accumulator 0 first and accumulator 1 a little later.  Row block 0
+          // therefore runs ahead over the first STAGES - 1 stages (which stay unreleased), then
+          // row block 1 catches up on the same stages and releases them.
+          const uint32_t pre = (kb_hi - kb_lo < static_cast<uint32_t>(STAGES - 1)) ? (kb_hi - kb_lo)
+                                                                                  : static_cast<uint32_t>(STAGES - 1);
+          uint32_t st = stage, ph = phase;
+          for (uint32_t i = 0; i < pre; ++i) {
+            const long long w1 = PROF ? clock64() : 0;
+            const bool got = detail::wait(full_bar(st), ph, ab, WAIT_MMA_FULL, t, kb_lo + i);
+            ok = __all_sync(0xFFFFFFFFu, got);
+            if (!ok) break;
+            const long long w2 = PROF ? clock64() : 0;
+            if constexpr (PROF) prof_full += w2 - w1;
+            ptx::tc_fence_after_sync();
+            if (ptx::elect_one()) issue_block(0, kb_lo + i, st);
+            __syncwarp();
+            if constexpr (PROF) prof_issue += clock64() - w2;
+            issued = true;
+            if (++st == STAGES) {
+              st = 0;
+              ph ^= 1u;
+            }
+          }
+          if (!ok) break;
+          const long long w3 = PROF ? clock64() : 0;
+          const bool got1 = detail::wait(tmem_empty_bar(1), acc_phase ^ 1u, ab,
+                                                    WAIT_MMA_TMEM_EMPTY, t, 1);
+          ok = __all_sync(0xFFFFFFFFu, got1);
+          if (!ok) break;
+          const long long w4 = PROF ? clock64() : 0;
+          if constexpr (PROF) {
+            prof_tmem += w4 - w3;
+            prof_tmem1 += w4 - w3;
+          }
+          ptx::tc_fence_after_sync();
+          for (uint32_t i = 0; i < pre; ++i) {
+            if (ptx::elect_one()) {
+              issue_block(1, kb_lo + i, stage);
+              release_stage(stage);
+            }
+            __syncwarp();
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          if constexpr (PROF) prof_issue += clock64() - w4;
+          kb = kb_lo + pre;
+        }
+        for (; kb < kb_hi; ++kb) {
           const long long w1 = PROF ? clock64() : 0;
           const bool got = detail::wait(full_bar(stage), phase, ab, WAIT_MMA_FULL, t, kb);
           ok = __all_sync(0xFFFFFFFFu, got);
@@ -595,25 +762,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           if constexpr (PROF) prof_full += w2 - w1;
           ptx::tc_fence_after_sync();
           if (ptx::elect_one()) {
-            const uint32_t a_lo = a_lo0 + stage * (Cfg::STAGE_BYTES >> 4);
-            const uint32_t b_lo = b_lo0 + stage * (Cfg::STAGE_BYTES >> 4);
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j) {  // 128 bytes of K per stage, 32 bytes per MMA
-              const uint64_t ad = (static_cast<uint64_t>(a_hi) << 32) | (a_lo + j * a_step);
-              const uint64_t bd = (static_cast<uint64_t>(b_hi) << 32) | (b_lo + j * b_step);
-              ptx::umma<Cfg::KIND, CTAS>(d_tmem, ad, bd, idesc_cur, (kb != kb_lo || j != 0u) ? 1u : 0u);
-            }
-            // Release the stage to the producer(s) once these MMAs have read it.
-            if constexpr (CTAS == 2) {
-              if (mcast) {
-                ptx::tc_commit_pair(empty_bar(stage));
-              } else {
-                ptx::tc_commit<CTAS>(empty_bar(stage));
-                ptx::tc_commit<CTAS>(ptx::mapa(empty_bar(stage), 1));
-              }
-            } else {
-              ptx::tc_commit<CTAS>(empty_bar(stage));
-            }
+            for (uint32_t mb = 0; mb < static_cast<uint32_t>(Cfg::MB); ++mb) issue_block(mb, kb, stage);
+            release_stage(stage);
           }
           __syncwarp();
           if constexpr (PROF) prof_issue += clock64() - w2;
@@ -625,20 +776,28 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
         if (!ok) break;
         if (!(p.test_flags & 1u) && ptx::elect_one()) {
-          if constexpr (CTAS == 2) {
-            if (mcast) {
-              ptx::tc_commit_pair(tmem_full_bar(acc));
+#pragma unroll
+          for (uint32_t mb = 0; mb < static_cast<uint32_t>(Cfg::MB); ++mb) {
+            const uint32_t fb = tmem_full_bar(acc + mb);
+            if constexpr (CTAS == 2) {
+              if (mcast) {
+                ptx::tc_commit_pair(fb);
+              } else {
+                ptx::tc_commit<CTAS>(fb);
+                ptx::tc_commit<CTAS>(ptx::mapa(fb, 1));
+              }
             } else {
-              ptx::tc_commit<CTAS>(tmem_full_bar(acc));
-              ptx::tc_commit<CTAS>(ptx::mapa(tmem_full_bar(acc), 1));
+              ptx::tc_commit<CTAS>(fb);
             }
-          } else {
-            ptx::tc_commit<CTAS>(tmem_full_bar(acc));
           }
         }
         __syncwarp();
-        acc ^= 1u;
-        if (acc == 0u) acc_phase ^= 1u;
+        if constexpr (Cfg::MB == 2) {
+          acc_phase ^= 1u;  // both accumulators are used by every tile
+        } else {
+          acc ^= 1u;
+          if (acc == 0u) acc_phase ^= 1u;
+        }
       }
       if constexpr (PROF) {
         if (lane == 0 && p.prof) {
@@ -647,6 +806,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           p.prof[16 * blockIdx.x + 4] = clock64() - prof_t0;
           p.prof[16 * blockIdx.x + 7] = ptx::globaltimer_ns() - prof_ns0;
           p.prof[16 * blockIdx.x + 9] = prof_issue;
+          p.prof[16 * blockIdx.x + 13] = prof_tmem1;
         }
       }
       if ((!ok || (p.test_flags & 1u)) && issued && lane == 0) {
@@ -660,6 +820,275 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
   } else {
     // ---------------------------------------------------------- epilogue
+    if constexpr (Cfg::MB == 2) {
+      // Two row blocks per CTA: eight warps, two per TMEM lane quadrant, each taking one half of
+      // the tile's columns.  The main loop of the next tile cannot start before accumulator 0 is
+      // free, so a warp first copies its whole share of an accumulator to registers, hands the
+      // accumulator back at once, and only then scales, casts and stores.
+      const uint32_t quad = warp & 3u;
+      const uint32_t half = warp >= 7u ? 1u : 0u;
+      const uint32_t stg = staging_base + (half * 4u + quad) * Cfg::STAGING_WARP_BYTES;
+      constexpr int BOX_COLS = 128 / sizeof(TOut);  // columns in one 128-byte staged row
+      constexpr int SLICES = BOX_COLS / 32;         // 32-column TMEM slices per staged box
+      constexpr int WORDS = 32 * sizeof(TOut) / 4;  // packed words per slice per row
+      constexpr int WARP_COLS = BN / 2;             // accumulator columns one warp holds at a time
+      constexpr int NSL = WARP_COLS / 32;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      const bool prof = PROF && p.prof != nullptr && warp == 2 && lane == 0;
+      long long prof_wait = 0, prof_copy = 0;
+      const long long prof_t0 = prof ? clock64() : 0;
+      const TOut* const cmat = static_cast<const TOut*>(p.c);
+      TOut* const dmat = static_cast<TOut*>(p.d);
+      const uint32_t tmem_empty_target =
+          (CTAS == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+      detail::WorkIter work(p, cluster, num_clusters, BN);
+      uint32_t t = 0, kb_lo = 0, kb_hi = 0;
+      while (ok && work.next(t, kb_lo, kb_hi)) {
+        uint32_t tm, tn;
+        tile_coords(p.grid, t, tm, tn);
+        const uint32_t wcols = work.cols / 2u;  // columns of this piece that belong to this warp
+        const uint32_t col_w = tn * BN + work.col_off + half * wcols;
+        if constexpr (sizeof(TOut) == 2) {
+          // 16-bit outputs without a C term: a warp's share of BOTH accumulators fits in its
+          // registers once packed (2 x 64 words), so both accumulators go back to the MMA warp
+          // before a single byte is stored; the stores then drain under the next main loop.
+          // (All CTAs finish their tiles at about the same time, so the burst of output stores
+          // is slow to drain; it must not hold up tensor memory.)
+          const bool plain = detail::OutTraits<TOut>::INT ? false : (p.beta_f == 0.0f);
+          if (plain && wcols == static_cast<uint32_t>(WARP_COLS) && col_w + WARP_COLS <= p.n &&
+              (p.epilogue_tma || p.d_vec_ok)) {
+            uint32_t y[2][NSL][16];
+            const uint32_t taddr0 = tmem_base + ((quad * 32u) << 16) + half * wcols;
+            const uint32_t row00 = tm * (Cfg::BM * CTAS) + rank * Cfg::BM + quad * 32u;
+            const long long w0 = prof ? clock64() : 0;
+            if (!detail::wait(tmem_full_bar(0), acc_phase, ab, WAIT_EPILOGUE_TMEM_FULL, t, 0)) {
+              ok = false;
+              break;
+            }
+            const long long c0 = prof ? clock64() : 0;
+            if (prof) prof_wait += c0 - w0;
+            ptx::tc_fence_after_sync();
+            {
+              uint32_t v[NSL][32];
+#pragma unroll
+              for (int sl = 0; sl < NSL; ++sl) ptx::tmem_ld_32x32(taddr0 + sl * 32u, v[sl]);
+              ptx::tmem_wait_ld();
+              ptx::tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) {
+                if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(tmem_empty_target);
+                else ptx::mbar_arrive(tmem_empty_target);
+              }
+#pragma unroll
+              for (int sl = 0; sl < NSL; ++sl) {
+                detail::scale_slice_in_place<TOut, false>(v[sl], p, nullptr);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) y[0][sl][i] = v[sl][i];
+              }
+            }
+            if (!detail::wait(tmem_full_bar(1), acc_phase, ab, WAIT_EPILOGUE_TMEM_FULL, t, 1)) {
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after_sync();
+#pragma unroll
+            for (int sl = 0; sl < NSL; ++sl) {
+              uint32_t x[32];
+              ptx::tmem_ld_32x32(taddr0 + BN + sl * 32u, x);
+              ptx::tmem_wait_ld();
+              detail::scale_slice_in_place<TOut, false>(x, p, nullptr);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) y[1][sl][i] = x[i];
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(tmem_empty_target + 8u);
+              else ptx::mbar_arrive(tmem_empty_target + 8u);
+            }
+            if (prof) prof_copy += clock64() - c0;
+            // Both accumulators are free; drain the registers.
+#pragma unroll
+            for (int mb = 0; mb < 2; ++mb) {
+              const uint32_t row0 = row00 + mb * 128u;
+              if (row0 >= p.m) break;
+              const bool row_ok = row0 + lane < p.m;
+              TOut* drow = dmat + static_cast<int64_t>(row0 + lane) * p.ldd + col_w;
+#pragma unroll
+              for (int box = 0; box < WARP_COLS / BOX_COLS; ++box) {
+                if (p.epilogue_tma) {
+                  // One staging box per warp: the store issued from it must have read it out.
+                  if (lane == 0) ptx::bulk_wait_group_read<0>();
+                  __syncwarp();
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {  // 16-byte chunk j of the staged row
+                    const uint32_t(&x)[16] = y[mb][box * SLICES + j / 4];
+                    const uint32_t addr = stg + lane * 128u + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x[4 * (j % 4)]),
+                                 "r"(x[4 * (j % 4) + 1]), "r"(x[4 * (j % 4) + 2]), "r"(x[4 * (j % 4) + 3])
+                                 : "memory");
+                  }
+                  ptx::fence_proxy_async_smem();
+                  __syncwarp();
+                  if (lane == 0) {
+                    ptx::tma_store_2d(&tm_d, stg, static_cast<int32_t>(col_w + box * BOX_COLS),
+                                      static_cast<int32_t>(row0));
+                    ptx::bulk_commit_group();
+                  }
+                } else if (row_ok) {
+                  uint4* d4 = reinterpret_cast<uint4*>(drow + box * BOX_COLS);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    const uint32_t(&x)[16] = y[mb][box * SLICES + j / 4];
+                    d4[j] = make_uint4(x[4 * (j % 4)], x[4 * (j % 4) + 1], x[4 * (j % 4) + 2], x[4 * (j % 4) + 3]);
+                  }
+                }
+              }
+            }
+            acc_phase ^= 1u;
+            continue;
+          }
+        }
+#pragma unroll 1
+        for (uint32_t mb = 0; mb < 2u; ++mb) {
+          const long long w0 = prof ? clock64() : 0;
+          if (!detail::wait(tmem_full_bar(mb), acc_phase, ab, WAIT_EPILOGUE_TMEM_FULL, t, mb)) {
+            ok = false;
+            break;
+          }
+          const long long c0 = prof ? clock64() : 0;
+          if (prof) prof_wait += c0 - w0;
+          ptx::tc_fence_after_sync();
+          const uint32_t row0 = tm * (Cfg::BM * CTAS) + rank * Cfg::BM + mb * 128u + quad * 32u;
+          const uint32_t row = row0 + lane;
+          const bool row_ok = row < p.m;
+          const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + mb * BN + half * wcols;
+          const bool has_beta = detail::OutTraits<TOut>::INT ? (p.beta_i != 0) : (p.beta_f != 0.0f);
+          // Fast path: this warp's whole share lies inside the matrix and C / D rows can be
+          // accessed in 16-byte vectors.  Everything else (edge tiles, tail strips, unaligned
+          // operands) takes the slice-by-slice path below, which frees the accumulator last.
+          const bool fast = wcols == static_cast<uint32_t>(WARP_COLS) && col_w + WARP_COLS <= p.n &&
+                            (p.epilogue_tma || p.d_vec_ok) && (!has_beta || p.c_vec_ok);
+          if (fast) {
+            uint32_t v[NSL][32];
+#pragma unroll
+            for (int sl = 0; sl < NSL; ++sl) ptx::tmem_ld_32x32(taddr + sl * 32u, v[sl]);
+            ptx::tmem_wait_ld();
+            // The accumulator is in registers: the MMA warp may overwrite it.
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(tmem_empty_target + 8u * mb);
+              else ptx::mbar_arrive(tmem_empty_target + 8u * mb);
+            }
+            if (prof) prof_copy += clock64() - c0;
+            if (row0 < p.m) {
+              const TOut* crow = cmat + static_cast<int64_t>(row) * p.ldc + col_w;
+              TOut* drow = dmat + static_cast<int64_t>(row) * p.ldd + col_w;
+#pragma unroll
+              for (int box = 0; box < WARP_COLS / BOX_COLS; ++box) {
+                if (p.epilogue_tma) {
+                  // One staging box per warp: the store issued from it must have read it out.
+                  if (lane == 0) ptx::bulk_wait_group_read<0>();
+                  __syncwarp();
+                }
+#pragma unroll
+                for (int sl = 0; sl < SLICES; ++sl) {
+                  uint32_t(&x)[32] = v[box * SLICES + sl];
+                  const int c_off = box * BOX_COLS + sl * 32;
+                  if (has_beta) {
+                    if (row_ok) detail::scale_slice_in_place<TOut, true>(x, p, crow + c_off);
+                  } else {
+                    detail::scale_slice_in_place<TOut, false>(x, p, nullptr);
+                  }
+                  if (p.epilogue_tma) {
+#pragma unroll
+                    for (int q = 0; q < WORDS / 4; ++q) {
+                      const uint32_t j = static_cast<uint32_t>(sl * (WORDS / 4) + q);
+                      const uint32_t addr = stg + lane * 128u + ((j ^ (lane & 7u)) << 4);
+                      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x[4 * q]),
+                                   "r"(x[4 * q + 1]), "r"(x[4 * q + 2]), "r"(x[4 * q + 3])
+                                   : "memory");
+                    }
+                  } else if (row_ok) {
+                    uint4* d4 = reinterpret_cast<uint4*>(drow + c_off);
+#pragma unroll
+                    for (int q = 0; q < WORDS / 4; ++q)
+                      d4[q] = make_uint4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+                  }
+                }
+                if (p.epilogue_tma) {
+                  ptx::fence_proxy_async_smem();
+                  __syncwarp();
+                  if (lane == 0) {
+                    ptx::tma_store_2d(&tm_d, stg, static_cast<int32_t>(col_w + box * BOX_COLS),
+                                      static_cast<int32_t>(row0));
+                    ptx::bulk_commit_group();
+                  }
+                }
+              }
+            }
+          } else {
+            if (row0 < p.m) {
+              for (uint32_t box = 0; box * BOX_COLS < wcols; ++box) {
+                const uint32_t box_col = col_w + box * BOX_COLS;
+                if (box_col >= p.n) break;
+                if (p.epilogue_tma) {
+                  if (lane == 0) ptx::bulk_wait_group_read<0>();
+                  __syncwarp();
+                }
+#pragma unroll 1
+                for (int sl = 0; sl < SLICES; ++sl) {
+                  const uint32_t col0 = box_col + sl * 32u;
+                  if (col0 >= p.n) break;  // uniform across the warp
+                  const uint32_t ncols = (p.n - col0 < 32u) ? (p.n - col0) : 32u;
+                  uint32_t x[32];
+                  ptx::tmem_ld_32x32(taddr + box * BOX_COLS + sl * 32u, x);
+                  ptx::tmem_wait_ld();
+                  const TOut* crow = cmat + static_cast<int64_t>(row) * p.ldc + col0;
+                  detail::epilogue_math<TOut>(x, p, crow, row_ok, ncols);
+                  if (p.epilogue_tma) {
+#pragma unroll
+                    for (int q = 0; q < WORDS / 4; ++q) {
+                      const uint32_t j = static_cast<uint32_t>(sl * (WORDS / 4) + q);
+                      const uint32_t addr = stg + lane * 128u + ((j ^ (lane & 7u)) << 4);
+                      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x[4 * q]),
+                                   "r"(x[4 * q + 1]), "r"(x[4 * q + 2]), "r"(x[4 * q + 3])
+                                   : "memory");
+                    }
+                  } else if (row_ok) {
+                    TOut* drow = dmat + static_cast<int64_t>(row) * p.ldd + col0;
+                    detail::store_direct<TOut>(x, drow, ncols, p.d_vec_ok != 0u);
+                  }
+                }
+                if (p.epilogue_tma) {
+                  ptx::fence_proxy_async_smem();
+                  __syncwarp();
+                  if (lane == 0) {
+                    ptx::tma_store_2d(&tm_d, stg, static_cast<int32_t>(box_col), static_cast<int32_t>(row0));
+                    ptx::bulk_commit_group();
+                  }
+                }
+              }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(tmem_empty_target + 8u * mb);
+              else ptx::mbar_arrive(tmem_empty_target + 8u * mb);
+            }
+          }
+        }
+        acc_phase ^= 1u;  // both accumulators are used by every tile
+      }
+      if (p.epilogue_tma && lane == 0) ptx::bulk_wait_group<0>();
+      if (prof) {
+        p.prof[16 * blockIdx.x + 5] = prof_wait;
+        p.prof[16 * blockIdx.x + 6] = clock64() - prof_t0;
+        p.prof[16 * blockIdx.x + 12] = prof_copy;
+      }
+    } else {
     const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) are readable by this warp
     const uint32_t ew = warp - 2u;
     const uint32_t stg = staging_base + ew * Cfg::STAGING_WARP_BYTES;
@@ -872,8 +1301,11 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
       // This accumulator may now be overwritten by the MMA warp.
       ptx::tc_fence_before_sync();
-      if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(tmem_empty_target + 8u * acc);
-      else ptx::mbar_arrive(tmem_empty_target + 8u * acc);
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(tmem_empty_target + 8u * acc);
+        else ptx::mbar_arrive(tmem_empty_target + 8u * acc);
+      }
       acc ^= 1u;
       if (acc == 0u) acc_phase ^= 1u;
     }
@@ -882,6 +1314,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       p.prof[16 * blockIdx.x + 5] = prof_wait;
       p.prof[16 * blockIdx.x + 6] = clock64() - prof_t0;
       p.prof[16 * blockIdx.x + 12] = prof_park;
+    }
     }
   }
 

@@ -91,6 +91,9 @@ typedef enum gz_config {
   GZ_CFG_SWAP_M32 = 7,
   GZ_CFG_SWAP_M64 = 8,
   GZ_CFG_SWAP_M128 = 9,
+  /* 512x256 tile on a 2-CTA pair: each CTA holds two 128-row blocks of A against its half of B, so
+   * a quarter less operand data moves per flop than with GZ_CFG_2CTA_N256.  For large problems. */
+  GZ_CFG_2CTA_M512_N256 = 10,
   GZ_CFG_SIMT = 15      /* plain CUDA-core kernel; chosen automatically when TMA alignment rules fail */
 } gz_config;
 

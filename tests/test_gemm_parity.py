@@ -12,7 +12,8 @@ pytestmark = pytest.mark.gpu
 F16, BF16, F32, S8, S32 = gz.DT_F16, gz.DT_BF16, gz.DT_F32, gz.DT_S8, gz.DT_S32
 E4M3, E5M2 = gz.DT_E4M3, gz.DT_E5M2
 DIRECT, TMA = gz.FLAG_EPILOGUE_DIRECT, gz.FLAG_EPILOGUE_TMA
-TC_CONFIGS = [gz.CFG_1CTA_N256, gz.CFG_1CTA_N128, gz.CFG_1CTA_N64, gz.CFG_2CTA_N256, gz.CFG_2CTA_N128]
+TC_CONFIGS = [gz.CFG_1CTA_N256, gz.CFG_1CTA_N128, gz.CFG_1CTA_N64, gz.CFG_2CTA_N256, gz.CFG_2CTA_N128,
+              gz.CFG_2CTA_M512_N256]
 
 
 def run(case):
@@ -38,7 +39,7 @@ def test_every_dtype_pair_k_major(config, in_t, out_t):
 
 @pytest.mark.parametrize("a_col,b_col", [(False, False), (True, False), (True, True), (False, True)])
 @pytest.mark.parametrize("in_t,out_t", [(BF16, F32), (F16, F16), (F32, F32), (S8, S32)])
-@pytest.mark.parametrize("config", [gz.CFG_1CTA_N256, gz.CFG_2CTA_N256, gz.CFG_1CTA_N128])
+@pytest.mark.parametrize("config", [gz.CFG_1CTA_N256, gz.CFG_2CTA_N256, gz.CFG_1CTA_N128, gz.CFG_2CTA_M512_N256])
 def test_every_layout(a_col, b_col, in_t, out_t, config):
     dist = "full" if in_t == S8 else "int"
     run(Case(in_t, out_t, 384, 512, 384, a_col=a_col, b_col=b_col, config=config, dist=dist, alpha=1, beta=1))
@@ -172,7 +173,9 @@ def test_split_k_is_reproducible_and_reusable():
                                         (gz.CFG_2CTA_N256, 2048, 3328),   # 104 tiles: 30 tail tiles in 2 strips
                                         (gz.CFG_1CTA_N256, 2048, 2560 + 256),  # 176 tiles on 148 CTAs
                                         (gz.CFG_1CTA_N128, 2176, 1280),   # 170 tiles: 22 tail tiles, 2 strips of 64
-                                        (gz.CFG_2CTA_N128, 2560, 1024 + 128)])
+                                        (gz.CFG_2CTA_N128, 2560, 1024 + 128),
+                                        (gz.CFG_2CTA_M512_N256, 3072, 3584),  # 84 tiles of 512x256: 10 tail tiles in 4 strips
+                                        (gz.CFG_2CTA_M512_N256, 4096, 3328)])  # 104 tiles: 30 tail tiles in 2 strips
 @pytest.mark.parametrize("in_t,out_t,b_col", [(BF16, BF16, True), (BF16, F32, False), (F32, F32, False),
                                               (S8, S32, True)])
 def test_tail_wave_is_cut_into_column_strips(config, m, n, in_t, out_t, b_col):

@@ -88,8 +88,21 @@ def test_misaligned_leading_dimension_selects_simt_kernel():
 
 def test_auto_configuration_choices():
     st, info = gz.validate(_desc(m=8192, n=8192, k=8192, layout_b=gz.COL_MAJOR), 148)
-    assert st == 0 and info.config == gz.CFG_2CTA_N256 and info.grid == 148 and info.tiles == 1024
-    assert info.smem_bytes <= 227 * 1024
+    # large 16-bit problem: 512x256 tiles (two row blocks per CTA), 7 waves of 74 CTA pairs
+    assert st == 0 and info.config == gz.CFG_2CTA_M512_N256 and info.grid == 148 and info.tiles == 512
+    assert info.tile_m == 512 and info.tile_n == 256 and 200 * 1024 < info.smem_bytes <= 227 * 1024
+    # aligned D rows leave through shared memory and TMA stores unless the caller asks otherwise
+    assert info.epilogue_tma == 1
+    st, info = gz.validate(_desc(m=8192, n=8192, k=8192, layout_b=gz.COL_MAJOR, flags=gz.FLAG_EPILOGUE_DIRECT), 148)
+    assert st == 0 and info.epilogue_tma == 0
+    st, info = gz.validate(_desc(m=256, n=250, k=64, layout_b=gz.COL_MAJOR), 148)  # 500-byte rows of D
+    assert st == 0 and info.epilogue_tma == 0
+    # 4-byte outputs cannot park both accumulators in registers: 256-row tiles
+    st, info = gz.validate(_desc(in_type=gz.DT_S8, out_type=gz.DT_S32, m=8192, n=8192, k=8192, layout_b=gz.COL_MAJOR), 148)
+    assert st == 0 and info.config == gz.CFG_2CTA_N256 and info.tiles == 1024
+    # too few tiles for the larger tile to pay
+    st, info = gz.validate(_desc(m=4096, n=4096, k=4096, layout_b=gz.COL_MAJOR), 148)
+    assert st == 0 and info.config == gz.CFG_2CTA_N256
     st, info = gz.validate(_desc(m=16, n=14336, k=4096, layout_b=gz.COL_MAJOR), 148)
     assert st == 0 and info.ctas_per_tile == 1 and info.grid <= 148
     # s8 with N-contiguous B needs a 128-column chunk per CTA: the 2-CTA 128-wide tile is refused

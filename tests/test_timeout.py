@@ -12,7 +12,7 @@ from tests.helpers import Case, check
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("config", [gz.CFG_1CTA_N128, gz.CFG_2CTA_N256])
+@pytest.mark.parametrize("config", [gz.CFG_1CTA_N128, gz.CFG_2CTA_N256, gz.CFG_2CTA_M512_N256])
 def test_withheld_signal_times_out_and_context_survives(config):
     m, n, k = 512, 512, 256
     a = torch.ones(m, k, dtype=torch.bfloat16, device="cuda:0")
