@@ -43,8 +43,8 @@ M = N = K = 8192
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the bench kernel
-# (profiles/sm100_gemm_bf16_8192_2cta.md); algorithmic bytes are 3 * 128 MiB.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.185e9
+# (profiles/sm100_gemm_bf16_8192_512x256.md); algorithmic bytes are 3 * 128 MiB.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.037e9
 
 
 def load_peaks():

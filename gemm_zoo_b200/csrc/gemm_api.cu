@@ -191,8 +191,8 @@ int tail_parts_for(const Problem& pr, const CfgShape& s, int64_t tiles, int64_t 
     if (strip < 64 || rem * f > units) break;
     if (pr.b_mn_major && (strip / s.ctas) % chunk != 0) break;  // N-contiguous B is fetched in 128-byte chunks
     if ((strip / s.ctas) % 8 != 0) break;
-    // two-row-block tiles: each epilogue warp stores whole 128-byte boxes of its half of the strip
-    if (s.mb == 2 && (strip / 2) % (128 / pr.out_size) != 0) break;
+    // with eight epilogue warps each stores whole 128-byte boxes of its half of the strip
+    if (s.bn >= 128 && (strip / 2) % (128 / pr.out_size) != 0) break;
     parts = f;
   }
   if (parts > 1) *first = tiles - rem;
@@ -256,7 +256,11 @@ int choose_config(const Problem& pr, int sm_count) {
       const double waves = parts > 1 ? double(first / units) + 1.0 / parts : double(cdiv(tiles, units));
       blocks_per_cta = waves * (double(k_blocks) + per_tile / per_block);
     }
-    const double cost = blocks_per_cta * per_block;
+    // Once per CTA: set-up and teardown (a CTA pair also synchronises as a cluster and allocates
+    // tensor memory jointly) and the last tile's epilogue, which nothing hides.  These decide
+    // between shapes when a CTA has only a handful of K blocks to do.
+    const double fixed = (s.ctas == 2 ? 3000.0 : 800.0) + 1500.0 + 8.0 * s.bn;
+    const double cost = blocks_per_cta * per_block + fixed;
     if (best == 0 || cost < best) {
       best = cost;
       best_cfg = s.config;
@@ -294,7 +298,7 @@ void fill_info(const Problem& pr, int config, int sm_count, gz_plan_info* info) 
   const int64_t units = sm_count / s->ctas;
   info->grid = (int32_t)((info->tiles < units ? info->tiles : units) * s->ctas);
   // Mirrors GemmCfg::SMEM_BYTES: alignment slack, the operand ring, epilogue staging, barriers.
-  const int staging = s->swap ? 0 : (s->mb == 2 ? 8 * 4096 : 4 * 2 * 4096);
+  const int staging = s->swap ? 0 : (s->bn >= 128 ? 8 : 4) * 4096;
   info->smem_bytes = 1024 + s->stages * (128 * s->mb * 128 + (s->bn / s->ctas) * 128) + staging + 256;
   // Output rows go through shared memory and TMA stores when D's row pitch allows it; the swapped
   // (skinny) tiles hold the transposed tile and always store straight from registers.

@@ -120,6 +120,7 @@ struct GemmParams {
   //  [12] epilogue warp 2: clocks parking split-K partial sums (two-row-block tiles: clocks copying
   //       accumulators to registers)
   //  [13] MMA: clocks waiting for the second accumulator of a two-row-block tile (part of [3])
+  //  [14] clocks from kernel entry to the end of set-up   [15] clocks from kernel entry to exit
   // Only kernels instantiated with PROF = true write them.
   unsigned long long* prof;
 };
@@ -148,9 +149,10 @@ struct GemmCfg {
   static constexpr int A_BYTES = BM * 128;       // one stage of A: BM rows x 128 bytes
   static constexpr int B_BYTES = BN_CTA * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int EPI_WARPS = MB == 2 ? 8 : 4;
-  // 32-row x 128-byte boxes per epilogue warp: two, or one where eight warps share the space
-  static constexpr int STAGING_WARP_BYTES = SWAP ? 0 : (MB == 2 ? 4096 : 2 * 4096);
+  // Epilogue warps: one per TMEM lane quadrant, or two (each taking half of the tile's columns)
+  // where a half is at least one 128-byte box wide for every output type.
+  static constexpr int EPI_WARPS = (!SWAP && BN >= 128) ? 8 : 4;
+  static constexpr int STAGING_WARP_BYTES = SWAP ? 0 : 4096;  // one 32-row x 128-byte box per warp
   static constexpr int STAGING_BYTES = EPI_WARPS * STAGING_WARP_BYTES;
   static constexpr int BAR_BYTES = 256;
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators (MB == 2: one per row block)
@@ -500,6 +502,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   constexpr int STAGES = Cfg::STAGES;
   constexpr int BN = Cfg::BN;
 
+  const long long kernel_t0 = PROF ? clock64() : 0;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // 128B-swizzle atoms need 1024-byte alignment
@@ -557,9 +560,11 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   }
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  if constexpr (PROF) {
+    if (p.prof && threadIdx.x == 32) p.prof[16 * blockIdx.x + 14] = clock64() - kernel_t0;
+  }
 
   const uint32_t k_blocks = p.k_blocks;
-  const uint32_t num_tiles = p.grid.num_tiles;
 
   if (warp == 0 || warp == 6) {
     // ---------------------------------------------------------- TMA producers
@@ -820,20 +825,24 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
   } else {
     // ---------------------------------------------------------- epilogue
-    if constexpr (Cfg::MB == 2) {
-      // Two row blocks per CTA: eight warps, two per TMEM lane quadrant, each taking one half of
-      // the tile's columns.  The main loop of the next tile cannot start before accumulator 0 is
-      // free, so a warp first copies its whole share of an accumulator to registers, hands the
-      // accumulator back at once, and only then scales, casts and stores.
+    if constexpr (!Cfg::SWAP) {
+      // Four or eight warps; a warp reads the TMEM lanes of its quadrant (warp % 4) and, with
+      // eight, one half of the tile's columns.  A warp first copies its whole share of an
+      // accumulator to registers and hands the accumulator back at once; only then does it
+      // scale, cast and store.  With two row blocks per CTA that hand-over is what the next
+      // tile's main loop waits for; with one it merely shortens the epilogue, which shows where
+      // a CTA has few tiles.
+      constexpr int HALVES = Cfg::EPI_WARPS / 4;
       const uint32_t quad = warp & 3u;
-      const uint32_t half = warp >= 7u ? 1u : 0u;
+      const uint32_t half = (HALVES == 2 && warp >= 7u) ? 1u : 0u;
       const uint32_t stg = staging_base + (half * 4u + quad) * Cfg::STAGING_WARP_BYTES;
       constexpr int BOX_COLS = 128 / sizeof(TOut);  // columns in one 128-byte staged row
       constexpr int SLICES = BOX_COLS / 32;         // 32-column TMEM slices per staged box
       constexpr int WORDS = 32 * sizeof(TOut) / 4;  // packed words per slice per row
-      constexpr int WARP_COLS = BN / 2;             // accumulator columns one warp holds at a time
+      constexpr int WARP_COLS = BN / HALVES;        // accumulator columns one warp holds at a time
       constexpr int NSL = WARP_COLS / 32;
-      uint32_t acc_phase = 0;
+      static_assert(WARP_COLS % BOX_COLS == 0 && NSL <= 4, "a warp's share: whole boxes, at most 128 registers");
+      uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
       const bool prof = PROF && p.prof != nullptr && warp == 2 && lane == 0;
       long long prof_wait = 0, prof_copy = 0;
@@ -847,9 +856,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       while (ok && work.next(t, kb_lo, kb_hi)) {
         uint32_t tm, tn;
         tile_coords(p.grid, t, tm, tn);
-        const uint32_t wcols = work.cols / 2u;  // columns of this piece that belong to this warp
+        const uint32_t wcols = work.cols / HALVES;  // columns of this piece that belong to this warp
         const uint32_t col_w = tn * BN + work.col_off + half * wcols;
-        if constexpr (sizeof(TOut) == 2) {
+        if constexpr (Cfg::MB == 2 && sizeof(TOut) == 2) {
           // 16-bit outputs without a C term: a warp's share of BOTH accumulators fits in its
           // registers once packed (2 x 64 words), so both accumulators go back to the MMA warp
           // before a single byte is stored; the stores then drain under the next main loop.
@@ -951,9 +960,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           }
         }
 #pragma unroll 1
-        for (uint32_t mb = 0; mb < 2u; ++mb) {
+        for (uint32_t mb = 0; mb < static_cast<uint32_t>(Cfg::MB); ++mb) {
+          const uint32_t ai = (Cfg::MB == 2) ? mb : acc;  // accumulator this row block was summed in
           const long long w0 = prof ? clock64() : 0;
-          if (!detail::wait(tmem_full_bar(mb), acc_phase, ab, WAIT_EPILOGUE_TMEM_FULL, t, mb)) {
+          if (!detail::wait(tmem_full_bar(ai), acc_phase, ab, WAIT_EPILOGUE_TMEM_FULL, t, mb)) {
             ok = false;
             break;
           }
@@ -963,7 +973,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           const uint32_t row0 = tm * (Cfg::BM * CTAS) + rank * Cfg::BM + mb * 128u + quad * 32u;
           const uint32_t row = row0 + lane;
           const bool row_ok = row < p.m;
-          const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + mb * BN + half * wcols;
+          const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + ai * BN + half * wcols;
           const bool has_beta = detail::OutTraits<TOut>::INT ? (p.beta_i != 0) : (p.beta_f != 0.0f);
           // Fast path: this warp's whole share lies inside the matrix and C / D rows can be
           // accessed in 16-byte vectors.  Everything else (edge tiles, tail strips, unaligned
@@ -979,8 +989,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
-              if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(tmem_empty_target + 8u * mb);
-              else ptx::mbar_arrive(tmem_empty_target + 8u * mb);
+              if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(tmem_empty_target + 8u * ai);
+              else ptx::mbar_arrive(tmem_empty_target + 8u * ai);
             }
             if (prof) prof_copy += clock64() - c0;
             if (row0 < p.m) {
@@ -1075,14 +1085,22 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
-              if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(tmem_empty_target + 8u * mb);
-              else ptx::mbar_arrive(tmem_empty_target + 8u * mb);
+              if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(tmem_empty_target + 8u * ai);
+              else ptx::mbar_arrive(tmem_empty_target + 8u * ai);
             }
           }
         }
-        acc_phase ^= 1u;  // both accumulators are used by every tile
+        if (!ok) break;
+        if constexpr (Cfg::MB == 2) {
+          acc_phase ^= 1u;  // both accumulators are used by every tile
+        } else {
+          acc ^= 1u;
+          if (acc == 0u) acc_phase ^= 1u;
+        }
       }
-      if (p.epilogue_tma && lane == 0) ptx::bulk_wait_group<0>();
+      // The CTA's shared memory must outlive the reads of its last TMA stores; the writes
+      // themselves complete on their own before the grid does.
+      if (p.epilogue_tma && lane == 0) ptx::bulk_wait_group_read<0>();
       if (prof) {
         p.prof[16 * blockIdx.x + 5] = prof_wait;
         p.prof[16 * blockIdx.x + 6] = clock64() - prof_t0;
@@ -1090,12 +1108,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
     } else {
     const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) are readable by this warp
-    const uint32_t ew = warp - 2u;
-    const uint32_t stg = staging_base + ew * Cfg::STAGING_WARP_BYTES;
-    constexpr int BOX_COLS = 128 / sizeof(TOut);  // columns in one 128-byte staged row
-    constexpr int SLICES = BOX_COLS / 32;         // 32-column TMEM slices per staged box
-    constexpr int WORDS = 32 * sizeof(TOut) / 4;  // packed words per slice per row
-    uint32_t acc = 0, acc_phase = 0, sbuf = 0;
+    uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     const bool prof = PROF && p.prof != nullptr && warp == 2 && lane == 0;
     long long prof_wait = 0, prof_park = 0;
@@ -1116,8 +1129,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
       if (prof) prof_wait += clock64() - w0;
       ptx::tc_fence_after_sync();
-      if constexpr (Cfg::SWAP) {
-        // Accumulator lane = output column (n), accumulator column = output row (m).
+      {
+        // Swapped operands: accumulator lane = output column (n), accumulator column = output row (m).
         const uint32_t ncol0 = tm * 128u + quad * 32u;  // first n of this warp
         const uint32_t ncol = ncol0 + lane;
         const bool n_ok = ncol < p.m;                   // p.m is the extent of the 128-row side (N)
@@ -1244,60 +1257,6 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             }
           }
         }
-      } else {
-        const uint32_t row0 = tm * (128u * CTAS) + rank * 128u + quad * 32u;  // first row of this warp
-        const uint32_t row = row0 + lane;
-        const bool row_ok = row < p.m;
-        const uint32_t col_tile = tn * BN + work.col_off;
-        const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
-        if (row0 < p.m) {
-          for (uint32_t box = 0; box < work.cols / BOX_COLS; ++box) {
-            const uint32_t box_col = col_tile + box * BOX_COLS;
-            if (box_col >= p.n) break;
-            const uint32_t sb_addr = stg + sbuf * 4096u;
-            if (p.epilogue_tma) {
-              // The buffer about to be overwritten was handed to a TMA store two boxes ago.
-              if (lane == 0) ptx::bulk_wait_group_read<1>();
-              __syncwarp();
-            }
-  #pragma unroll
-            for (int sl = 0; sl < SLICES; ++sl) {
-              const uint32_t col0 = box_col + sl * 32u;
-              if (col0 >= p.n) break;  // uniform across the warp
-              const uint32_t ncols = (p.n - col0 < 32u) ? (p.n - col0) : 32u;
-              uint32_t v[32];
-              ptx::tmem_ld_32x32(taddr + box * BOX_COLS + sl * 32u, v);
-              ptx::tmem_wait_ld();
-              const TOut* crow = cmat + static_cast<int64_t>(row) * p.ldc + col0;
-              detail::epilogue_math<TOut>(v, p, crow, row_ok, ncols);
-              if (p.epilogue_tma) {
-                // Row `lane` of the staged box; 16-byte chunk j lands at j ^ (lane % 8),
-                // the layout a 128B-swizzled tensor map expects.
-  #pragma unroll
-                for (int q = 0; q < WORDS / 4; ++q) {
-                  const uint32_t j = static_cast<uint32_t>(sl * (WORDS / 4) + q);
-                  const uint32_t addr = sb_addr + lane * 128u + ((j ^ (lane & 7u)) << 4);
-                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v[4 * q]),
-                               "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
-                               : "memory");
-                }
-              } else if (row_ok) {
-                TOut* drow = dmat + static_cast<int64_t>(row) * p.ldd + col0;
-                detail::store_direct<TOut>(v, drow, ncols, p.d_vec_ok != 0u);
-              }
-            }
-            if (p.epilogue_tma) {
-              ptx::fence_proxy_async_smem();
-              __syncwarp();
-              if (lane == 0) {
-                ptx::tma_store_2d(&tm_d, sb_addr, static_cast<int32_t>(box_col),
-                                  static_cast<int32_t>(row0));
-                ptx::bulk_commit_group();
-              }
-              sbuf ^= 1u;
-            }
-          }
-        }
       }
       // This accumulator may now be overwritten by the MMA warp.
       ptx::tc_fence_before_sync();
@@ -1309,7 +1268,6 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       acc ^= 1u;
       if (acc == 0u) acc_phase ^= 1u;
     }
-    if (p.epilogue_tma && lane == 0) ptx::bulk_wait_group<0>();
     if (prof) {
       p.prof[16 * blockIdx.x + 5] = prof_wait;
       p.prof[16 * blockIdx.x + 6] = clock64() - prof_t0;
@@ -1337,6 +1295,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
+  }
+  if constexpr (PROF) {
+    if (p.prof && threadIdx.x == 32) p.prof[16 * blockIdx.x + 15] = clock64() - kernel_t0;
   }
 }
 
