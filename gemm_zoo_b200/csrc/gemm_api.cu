@@ -57,6 +57,29 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Makes `device` current for the calling thread and puts the previous device back on scope exit:
+// no entry point of the library leaves the caller's current device changed.
+class DeviceGuard {
+ public:
+  explicit DeviceGuard(int device) {
+    ok_ = cudaGetDevice(&prev_) == cudaSuccess;
+    if (ok_ && prev_ != device) {
+      ok_ = cuda_ok(cudaSetDevice(device), "cudaSetDevice");
+      changed_ = ok_;
+    }
+  }
+  ~DeviceGuard() {
+    if (changed_) (void)cudaSetDevice(prev_);
+  }
+  DeviceGuard(const DeviceGuard&) = delete;
+  DeviceGuard& operator=(const DeviceGuard&) = delete;
+  bool ok() const { return ok_; }
+
+ private:
+  int prev_ = 0;
+  bool ok_ = false, changed_ = false;
+};
+
 int dtype_size(int dt) {
   switch (dt) {
     case GZ_DT_F16:
@@ -662,7 +685,8 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
   if (!cuda_ok(cudaGetDeviceProperties(&prop, pr.d.device), "cudaGetDeviceProperties"))
     return GZ_ERR_CUDA;
   if (prop.major != 10) return GZ_ERR_NO_DEVICE;
-  if (!cuda_ok(cudaSetDevice(pr.d.device), "cudaSetDevice")) return GZ_ERR_CUDA;
+  DeviceGuard guard(pr.d.device);
+  if (!guard.ok()) return GZ_ERR_CUDA;
 
   const int sm_count = prop.multiProcessorCount;
   int config = pr.d.config;
@@ -766,7 +790,7 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
 
 GZ_API gz_status gz_gemm_plan_destroy(gz_plan* pl) {
   if (!pl) return GZ_ERR_INVALID_ARG;
-  (void)cudaSetDevice(pl->pr.d.device);
+  DeviceGuard guard(pl->pr.d.device);
   if (pl->status_dev) cudaFree(pl->status_dev);
   if (pl->workspace) cudaFree(pl->workspace);
   if (pl->ha) cudaFree(pl->ha);
@@ -791,8 +815,8 @@ GZ_API gz_status gz_gemm_plan_set_profile(gz_plan* pl, void* device_words) {
   if (!pl) return GZ_ERR_INVALID_ARG;
   if (device_words) {
     if (!pl->entry.launch_prof) return GZ_ERR_UNSUPPORTED;
-    if (!cuda_ok(cudaSetDevice(pl->pr.d.device), "cudaSetDevice") ||
-        !cuda_ok(pl->entry.attr_prof(), "cudaFuncSetAttribute(max dynamic shared memory)"))
+    DeviceGuard guard(pl->pr.d.device);
+    if (!guard.ok() || !cuda_ok(pl->entry.attr_prof(), "cudaFuncSetAttribute(max dynamic shared memory)"))
       return GZ_ERR_CUDA;
   }
   pl->base.prof = static_cast<unsigned long long*>(device_words);
@@ -805,10 +829,28 @@ GZ_API gz_status gz_gemm_plan_info(const gz_plan* pl, gz_plan_info* info) {
   return GZ_OK;
 }
 
-GZ_API gz_status gz_gemm_run(gz_plan* pl, const void* a, const void* b, const void* c, void* d,
-                             const void* alpha, const void* beta, void* stream_v) {
+}  // extern "C"
+
+namespace {
+
+// Where a launch writes its output when not to one matrix: column block o of width `cols` goes to
+// ptrs[o] (row pitch ld elements).  Used by the K-sharded GEMM, whose pointers are peer memory.
+struct ScatterSpec {
+  uint32_t cols;
+  int parts;
+  int64_t ld;
+  void* ptrs[8];
+};
+
+gz_status run_impl(gz_plan* pl, const void* a, const void* b, const void* c, void* d, const void* alpha,
+                   const void* beta, void* stream_v, const ScatterSpec* sc) {
   if (!pl || !a || !b || !d) return GZ_ERR_INVALID_ARG;
   const Problem& pr = pl->pr;
+  if (sc) {
+    if (pl->info.config == GZ_CFG_SIMT || pr.out_size != 4 || sc->cols == 0 || sc->cols % 32 != 0 ||
+        sc->parts < 1 || sc->parts > 8 || (int64_t)sc->cols * sc->parts < pr.d.n || sc->ld < sc->cols)
+      return GZ_ERR_UNSUPPORTED;
+  }
   float af, bf;
   int32_t ai, bi;
   gz_status st = read_scalars(pr, alpha, beta, &af, &bf, &ai, &bi);
@@ -820,13 +862,12 @@ GZ_API gz_status gz_gemm_run(gz_plan* pl, const void* a, const void* b, const vo
       (c && misaligned(c, pr.out_size)))
     return GZ_ERR_MISALIGNED;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  int cur = -1;
-  if (cudaGetDevice(&cur) != cudaSuccess || cur != pr.d.device) {
-    if (!cuda_ok(cudaSetDevice(pr.d.device), "cudaSetDevice")) return GZ_ERR_CUDA;
-  }
+  DeviceGuard guard(pr.d.device);
+  if (!guard.ok()) return GZ_ERR_CUDA;
 
   const bool tma_ptr_ok = (reinterpret_cast<uintptr_t>(a) % 16 == 0) &&
                           (reinterpret_cast<uintptr_t>(b) % 16 == 0);
+  if (sc && !tma_ptr_ok) return GZ_ERR_MISALIGNED;
   if (pl->info.config == GZ_CFG_SIMT || !tma_ptr_ok) {
     gz::SimtParams sp;
     sp.a = a;
@@ -862,6 +903,17 @@ GZ_API gz_status gz_gemm_run(gz_plan* pl, const void* a, const void* b, const vo
   p.c_vec_ok = (c && reinterpret_cast<uintptr_t>(c) % 16 == 0 && (pr.d.ldc * pr.out_size) % 16 == 0) ? 1u : 0u;
   p.d_vec_ok = (reinterpret_cast<uintptr_t>(d) % 16 == 0 && (pr.d.ldd * pr.out_size) % 16 == 0) ? 1u : 0u;
   if (p.epilogue_tma && reinterpret_cast<uintptr_t>(d) % 16 != 0) p.epilogue_tma = 0;
+  if (sc) {
+    p.epilogue_tma = 0;
+    p.scatter_cols = sc->cols;
+    p.ldd = sc->ld;
+    bool vec = (sc->ld * pr.out_size) % 16 == 0;
+    for (int i = 0; i < 8; ++i) {
+      p.scatter_ptrs[i] = i < sc->parts ? sc->ptrs[i] : nullptr;
+      if (i < sc->parts && reinterpret_cast<uintptr_t>(sc->ptrs[i]) % 16 != 0) vec = false;
+    }
+    p.d_vec_ok = vec ? 1u : 0u;
+  }
 
   CUtensorMap ta, tb, td;
   const uint32_t bk = 128u / pr.in_size;
@@ -896,6 +948,15 @@ GZ_API gz_status gz_gemm_run(gz_plan* pl, const void* a, const void* b, const vo
   return GZ_OK;
 }
 
+}  // namespace
+
+extern "C" {
+
+GZ_API gz_status gz_gemm_run(gz_plan* pl, const void* a, const void* b, const void* c, void* d,
+                             const void* alpha, const void* beta, void* stream_v) {
+  return run_impl(pl, a, b, c, d, alpha, beta, stream_v, nullptr);
+}
+
 GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, const void* c, void* d,
                                   const void* alpha, const void* beta, void* stream_v) {
   if (!pl || !a || !b || !d) return GZ_ERR_INVALID_ARG;
@@ -906,7 +967,8 @@ GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, con
   if (st != GZ_OK) return st;
   const bool beta_zero = (pr.d.in_type == GZ_DT_S8) ? (bi == 0) : (bf == 0.0f);
   if (!beta_zero && !c) return GZ_ERR_INVALID_ARG;
-  if (!cuda_ok(cudaSetDevice(pr.d.device), "cudaSetDevice")) return GZ_ERR_CUDA;
+  DeviceGuard guard(pr.d.device);
+  if (!guard.ok()) return GZ_ERR_CUDA;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
   const size_t a_rows = pr.a_mn_major ? pr.d.k : pr.d.m;
@@ -1034,7 +1096,8 @@ GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, con
 GZ_API gz_status gz_last_device_status(gz_plan* pl, void* stream_v, uint32_t detail[4]) {
   if (!pl) return GZ_ERR_INVALID_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  if (!cuda_ok(cudaSetDevice(pl->pr.d.device), "cudaSetDevice")) return GZ_ERR_CUDA;
+  DeviceGuard guard(pl->pr.d.device);
+  if (!guard.ok()) return GZ_ERR_CUDA;
   uint32_t h[4] = {0, 0, 0, 0};
   if (!cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize") ||
       !cuda_ok(cudaMemcpy(h, pl->status_dev, sizeof(h), cudaMemcpyDeviceToHost), "read status"))
@@ -1109,6 +1172,12 @@ extern "C" GZ_API gz_status gz_fill(void* ptr, int32_t dtype, int64_t count, uin
   if (!ptr || count < 0 || dist < 0 || dist > 2 || dtype_size(dtype) == 0) return GZ_ERR_INVALID_ARG;
   if (count == 0) return GZ_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  // The kernel runs on the GPU that owns the buffer, whatever the caller's current device.
+  cudaPointerAttributes attr;
+  if (!cuda_ok(cudaPointerGetAttributes(&attr, ptr), "cudaPointerGetAttributes")) return GZ_ERR_CUDA;
+  if (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged) return GZ_ERR_INVALID_ARG;
+  DeviceGuard guard(attr.device);
+  if (!guard.ok()) return GZ_ERR_CUDA;
   const int block = 256;
   int64_t want = cdiv(count, block);
   const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
@@ -1178,7 +1247,8 @@ gz_status static_scratch_setup(int device, StaticScratchDevice** out) {
         !cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "device attribute"))
       return GZ_ERR_CUDA;
     if (major != 10) return GZ_ERR_NO_DEVICE;
-    if (!cuda_ok(cudaSetDevice(device), "cudaSetDevice")) return GZ_ERR_CUDA;
+    DeviceGuard guard(device);  // the symbol's address is taken with its device current
+    if (!guard.ok()) return GZ_ERR_CUDA;
     void* ptr = nullptr;
     if (!cuda_ok(cudaGetSymbolAddress(&ptr, g_static_scratch), "cudaGetSymbolAddress(static scratch)") || !ptr)
       return GZ_ERR_CUDA;
@@ -1218,10 +1288,8 @@ extern "C" GZ_API gz_status gz_gemm_skinny_static(const gz_gemm_desc* desc, cons
   StaticScratchDevice* sd = nullptr;
   st = static_scratch_setup(pr.d.device, &sd);
   if (st != GZ_OK) return st;
-  int cur = -1;
-  if (cudaGetDevice(&cur) != cudaSuccess || cur != pr.d.device) {
-    if (!cuda_ok(cudaSetDevice(pr.d.device), "cudaSetDevice")) return GZ_ERR_CUDA;
-  }
+  DeviceGuard guard(pr.d.device);
+  if (!guard.ok()) return GZ_ERR_CUDA;
 
   int config = pr.d.config;
   if (config == GZ_CFG_AUTO)
@@ -1305,3 +1373,6 @@ extern "C" GZ_API gz_status gz_gemm_skinny_static(const gz_gemm_desc* desc, cons
   if (!cuda_ok(entry.launch(ta, tb, ta, p, info.grid, stream), "kernel launch")) return GZ_ERR_CUDA;
   return GZ_OK;
 }
+
+// ------------------------------------------------------------------ K-sharded GEMM (multi-GPU)
+#include "ksharded.cuh"

@@ -108,6 +108,12 @@ struct GemmParams {
   unsigned long long total_kb;   // num_tiles * k_blocks
   float* ws;                     // [num_tiles][max_contrib][BN/4][128] float4 partial accumulators (fp32 or int32 bits)
   int* counters;                 // [num_tiles], zero between launches
+  // Scattered output (0 = off): output columns [o * scatter_cols, (o + 1) * scatter_cols) are written
+  // to the matrix at scatter_ptrs[o] (row pitch ldd, column index relative to the block) instead
+  // of d.  The pointers may be peer-GPU memory: a K-sharded GEMM pushes each column block of its
+  // partial sums straight to the GPU that owns the block.  Direct-store epilogue only.
+  uint32_t scatter_cols;
+  void* scatter_ptrs[8];
   // Tuning switches (see TUNE_* below).
   uint32_t tune;
   // Optional stall counters, 16 words per CTA (null = off):
@@ -429,6 +435,38 @@ __device__ __forceinline__ void store_direct(const uint32_t (&v)[32], TOut* drow
   }
 }
 
+
+// Address of output element (row, col); col must not be split from its 32-aligned neighbours by a
+// scatter boundary (scatter_cols is a multiple of 32).
+template <typename TOut>
+__device__ __forceinline__ TOut* out_ptr(const GemmParams& p, uint32_t row, uint32_t col) {
+  if (p.scatter_cols == 0u) return static_cast<TOut*>(p.d) + static_cast<int64_t>(row) * p.ldd + col;
+  const uint32_t owner = col / p.scatter_cols;
+  return static_cast<TOut*>(p.scatter_ptrs[owner]) + static_cast<int64_t>(row) * p.ldd +
+         (col - owner * p.scatter_cols);
+}
+
+// Write a staged 32-row x 128-byte box (rows 128-byte-swizzled, as a TMA store would read it) to
+// the output with plain stores: per instruction eight lanes cover one row's 128 bytes, so every
+// store instruction writes four whole 128-byte lines.  This is the store path when D cannot be
+// described to TMA and when the output is scattered to peer GPUs, where 16-byte fragments of
+// 32 different rows per instruction would waste the link.
+template <typename TOut>
+__device__ __forceinline__ void store_staged_box(const GemmParams& p, uint32_t stg, uint32_t lane, uint32_t row0,
+                                                 uint32_t box_col) {
+  constexpr uint32_t PER16 = 16 / sizeof(TOut);
+  const uint32_t j = lane & 7u;
+#pragma unroll
+  for (uint32_t i = 0; i < 8; ++i) {
+    const uint32_t r = i * 4u + (lane >> 3);
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(stg + r * 128u + ((j ^ (r & 7u)) << 4))
+                 : "memory");
+    if (row0 + r < p.m) *reinterpret_cast<uint4*>(out_ptr<TOut>(p, row0 + r, box_col + j * PER16)) = v;
+  }
+}
 
 // alpha * acc (+ beta * c) for one full 32-column slice of one row, in place and without a second
 // register array: on return x[0 .. 32 * sizeof(TOut) / 4) holds the packed outputs.  `crow` points
@@ -848,7 +886,6 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       long long prof_wait = 0, prof_copy = 0;
       const long long prof_t0 = prof ? clock64() : 0;
       const TOut* const cmat = static_cast<const TOut*>(p.c);
-      TOut* const dmat = static_cast<TOut*>(p.d);
       const uint32_t tmem_empty_target =
           (CTAS == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
       detail::WorkIter work(p, cluster, num_clusters, BN);
@@ -922,14 +959,14 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             for (int mb = 0; mb < 2; ++mb) {
               const uint32_t row0 = row00 + mb * 128u;
               if (row0 >= p.m) break;
-              const bool row_ok = row0 + lane < p.m;
-              TOut* drow = dmat + static_cast<int64_t>(row0 + lane) * p.ldd + col_w;
 #pragma unroll
               for (int box = 0; box < WARP_COLS / BOX_COLS; ++box) {
                 if (p.epilogue_tma) {
                   // One staging box per warp: the store issued from it must have read it out.
                   if (lane == 0) ptx::bulk_wait_group_read<0>();
                   __syncwarp();
+                }
+                {
 #pragma unroll
                   for (int j = 0; j < 8; ++j) {  // 16-byte chunk j of the staged row
                     const uint32_t(&x)[16] = y[mb][box * SLICES + j / 4];
@@ -938,6 +975,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                                  "r"(x[4 * (j % 4) + 1]), "r"(x[4 * (j % 4) + 2]), "r"(x[4 * (j % 4) + 3])
                                  : "memory");
                   }
+                }
+                if (p.epilogue_tma) {
                   ptx::fence_proxy_async_smem();
                   __syncwarp();
                   if (lane == 0) {
@@ -945,13 +984,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                                       static_cast<int32_t>(row0));
                     ptx::bulk_commit_group();
                   }
-                } else if (row_ok) {
-                  uint4* d4 = reinterpret_cast<uint4*>(drow + box * BOX_COLS);
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) {
-                    const uint32_t(&x)[16] = y[mb][box * SLICES + j / 4];
-                    d4[j] = make_uint4(x[4 * (j % 4)], x[4 * (j % 4) + 1], x[4 * (j % 4) + 2], x[4 * (j % 4) + 3]);
-                  }
+                } else {
+                  __syncwarp();
+                  detail::store_staged_box<TOut>(p, stg, lane, row0, col_w + box * BOX_COLS);
+                  __syncwarp();
                 }
               }
             }
@@ -995,7 +1031,6 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             if (prof) prof_copy += clock64() - c0;
             if (row0 < p.m) {
               const TOut* crow = cmat + static_cast<int64_t>(row) * p.ldc + col_w;
-              TOut* drow = dmat + static_cast<int64_t>(row) * p.ldd + col_w;
 #pragma unroll
               for (int box = 0; box < WARP_COLS / BOX_COLS; ++box) {
                 if (p.epilogue_tma) {
@@ -1012,20 +1047,13 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   } else {
                     detail::scale_slice_in_place<TOut, false>(x, p, nullptr);
                   }
-                  if (p.epilogue_tma) {
 #pragma unroll
-                    for (int q = 0; q < WORDS / 4; ++q) {
-                      const uint32_t j = static_cast<uint32_t>(sl * (WORDS / 4) + q);
-                      const uint32_t addr = stg + lane * 128u + ((j ^ (lane & 7u)) << 4);
-                      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x[4 * q]),
-                                   "r"(x[4 * q + 1]), "r"(x[4 * q + 2]), "r"(x[4 * q + 3])
-                                   : "memory");
-                    }
-                  } else if (row_ok) {
-                    uint4* d4 = reinterpret_cast<uint4*>(drow + c_off);
-#pragma unroll
-                    for (int q = 0; q < WORDS / 4; ++q)
-                      d4[q] = make_uint4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+                  for (int q = 0; q < WORDS / 4; ++q) {
+                    const uint32_t j = static_cast<uint32_t>(sl * (WORDS / 4) + q);
+                    const uint32_t addr = stg + lane * 128u + ((j ^ (lane & 7u)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x[4 * q]),
+                                 "r"(x[4 * q + 1]), "r"(x[4 * q + 2]), "r"(x[4 * q + 3])
+                                 : "memory");
                   }
                 }
                 if (p.epilogue_tma) {
@@ -1036,6 +1064,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                                       static_cast<int32_t>(row0));
                     ptx::bulk_commit_group();
                   }
+                } else {
+                  __syncwarp();
+                  detail::store_staged_box<TOut>(p, stg, lane, row0, col_w + box * BOX_COLS);
+                  __syncwarp();
                 }
               }
             }
@@ -1068,7 +1100,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                                    : "memory");
                     }
                   } else if (row_ok) {
-                    TOut* drow = dmat + static_cast<int64_t>(row) * p.ldd + col0;
+                    TOut* drow = detail::out_ptr<TOut>(p, row, col0);
                     detail::store_direct<TOut>(x, drow, ncols, p.d_vec_ok != 0u);
                   }
                 }
@@ -1114,7 +1146,6 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     long long prof_wait = 0, prof_park = 0;
     const long long prof_t0 = prof ? clock64() : 0;
     const TOut* const cmat = static_cast<const TOut*>(p.c);
-    TOut* const dmat = static_cast<TOut*>(p.d);
     const uint32_t tmem_empty_target =
         (CTAS == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
     detail::WorkIter work(p, cluster, num_clusters, BN);
@@ -1240,7 +1271,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               // Column i of the slice is output row mrow0 + i; for each, the 32 lanes of the warp
               // write 32 consecutive elements of that row.
               const uint32_t cnt = (p.n - mrow0 < 16u) ? (p.n - mrow0) : 16u;
-              TOut* dp = dmat + static_cast<int64_t>(mrow0) * p.ldd + ncol;
+              TOut* dp = detail::out_ptr<TOut>(p, mrow0, ncol);
               const TOut* cp = cmat + static_cast<int64_t>(mrow0) * p.ldc + ncol;
               if (has_beta) {
 #pragma unroll

@@ -25,6 +25,31 @@ def test_library_exports_every_declared_symbol():
     assert L.gz_version() >= 100
 
 
+def test_library_exports_every_k_sharded_symbol():
+    from gemm_zoo_b200 import ksharded
+    header = (ROOT / "include" / "gemmzoo" / "ksharded.h").read_text()
+    declared = re.findall(r"GZ_API\s+[\w\s\*]+?\b(gz_\w+)\s*\(", header)
+    L = gz.lib()
+    for name in declared:
+        assert hasattr(L, name), name
+    assert sorted(declared) == sorted(ksharded.EXPORTED_SYMBOLS)
+    # argument errors that need no GPU
+    d = ksharded.make_desc(gz.DT_BF16, gz.DT_BF16, 16, 1024, 512, world=2, rank=0)
+    assert ksharded.workspace_bytes(d) >= 2 * 2 * 16 * 512 * 4
+    bad = ksharded.make_desc(gz.DT_BF16, gz.DT_BF16, 16, 1000, 512, world=2, rank=0)  # 1000 % 64 != 0
+    with pytest.raises(gz.GzError) as e:
+        ksharded.workspace_bytes(bad)
+    assert e.value.status == api.GZ_ERR_UNSUPPORTED
+    for kw in (dict(world=9, rank=0), dict(world=2, rank=2), dict(world=0, rank=0)):
+        with pytest.raises(gz.GzError) as e:
+            ksharded.workspace_bytes(ksharded.make_desc(gz.DT_BF16, gz.DT_BF16, 16, 1024, 512, **kw))
+        assert e.value.status == api.GZ_ERR_INVALID_ARG
+    # K slices: aligned boundaries that cover K exactly
+    bounds = [ksharded.k_slice(4096 + 64, 8, r) for r in range(8)]
+    assert bounds[0][0] == 0 and bounds[-1][1] == 4096 + 64
+    assert all(bounds[i][1] == bounds[i + 1][0] and bounds[i][1] % 64 == 0 for i in range(7))
+
+
 def test_status_strings():
     for s in range(0, 9):
         assert len(gz.status_string(s)) > 1

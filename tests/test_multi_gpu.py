@@ -37,3 +37,39 @@ def test_partition_across_devices_bitwise():
             shards.append(d.cpu())
     got = torch.cat(shards, dim=1)
     assert torch.equal(got.view(torch.int16), full.cpu().view(torch.int16))
+
+
+def test_entry_points_leave_the_current_device_alone():
+    """Plans for another GPU are created, run, queried and destroyed while device 0 stays the
+    calling thread's current device, and gz_fill runs on the GPU that owns the buffer."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    import ctypes as C
+    rt = C.CDLL("libcudart.so.12")
+    def current():
+        d = C.c_int(-1)
+        assert rt.cudaGetDevice(C.byref(d)) == 0
+        return d.value
+    torch.cuda.set_device(0)
+    assert current() == 0
+    m, n, k = 256, 512, 256
+    a = torch.empty(m, k, dtype=torch.bfloat16, device="cuda:1")
+    b = torch.empty(n, k, dtype=torch.bfloat16, device="cuda:1")
+    gz.fill(a, 3, 1, 2, 3.0)
+    gz.fill(b, 3, 2, 2, 3.0)
+    assert current() == 0
+    d = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda:1")
+    g = gz.Sm100Gemm(m, n, k, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR, device=1)
+    assert current() == 0
+    g(a, b, None, d, 1.0, 0.0)
+    assert current() == 0
+    assert g.plan.device_status()[0] == 0 and current() == 0
+    g.plan.destroy()
+    assert current() == 0
+    want = (a.double() @ b.double().t()).to(torch.bfloat16)
+    assert torch.equal(d.cpu(), want.cpu())
+    # device 0 work right after is unaffected
+    x = torch.empty(1 << 12, dtype=torch.float32, device="cuda:0")
+    gz.fill(x, 1, 1, 0)
+    torch.cuda.synchronize()
+    assert x.abs().max().item() <= 1.0
