@@ -14,6 +14,7 @@ from .api import (  # noqa: F401
     FLAG_EPILOGUE_DIRECT, FLAG_EPILOGUE_TMA, FLAG_TEST_WITHHOLD_ACC_READY, FLAG_NO_SPLIT_K, FLAG_SPLIT_K,
     GemmDesc, GzError, Plan, PlanInfo, Sm100Gemm, fill, lib, lib_path, partition_columns,
     status_string, tile_coords, validate, EXPORTED_SYMBOLS, gemm_skinny_static, STATIC_SCRATCH_BYTES,
+    ACT_NONE, ACT_RELU, ACT_GELU, ACT_GELU_TANH, ACT_SILU, Epilogue,
 )
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -26,9 +26,26 @@ GZ_ERR_DEVICE_TIMEOUT, GZ_ERR_NO_DEVICE, GZ_ERR_TOO_LARGE, GZ_ERR_OUT_OF_MEMORY 
 EXPORTED_SYMBOLS = [
     "gz_gemm_desc_validate", "gz_gemm_plan_create", "gz_gemm_plan_destroy", "gz_gemm_plan_info",
     "gz_gemm_plan_set_profile",
-    "gz_gemm_run", "gz_gemm_run_host", "gz_gemm_skinny_static", "gz_last_device_status", "gz_status_string",
+    "gz_gemm_run", "gz_gemm_run_ex", "gz_gemm_run_host", "gz_gemm_skinny_static", "gz_last_device_status", "gz_status_string",
     "gz_last_cuda_error", "gz_fill", "gz_tile_coords", "gz_partition_columns", "gz_version",
 ]
+
+
+ACT_NONE, ACT_RELU, ACT_GELU, ACT_GELU_TANH, ACT_SILU = 0, 1, 2, 3, 4
+
+
+class Epilogue(C.Structure):
+    """gz_epilogue: D = act(alpha * row_scale[i] * col_scale[j] * acc + beta * C + bias[j])."""
+    _fields_ = [("struct_size", C.c_uint32), ("activation", C.c_int32), ("bias", C.c_void_p),
+                ("row_scale", C.c_void_p), ("col_scale", C.c_void_p)]
+
+    @classmethod
+    def make(cls, bias=None, row_scale=None, col_scale=None, activation=ACT_NONE):
+        e = cls()
+        e.struct_size = C.sizeof(cls)
+        e.activation = activation
+        e.bias, e.row_scale, e.col_scale = _ptr(bias), _ptr(row_scale), _ptr(col_scale)
+        return e
 
 
 class GemmDesc(C.Structure):
@@ -106,6 +123,8 @@ def lib():
     L.gz_gemm_plan_info.restype = C.c_int
     L.gz_gemm_run.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp]
     L.gz_gemm_run.restype = C.c_int
+    L.gz_gemm_run_ex.argtypes = [vp, vp, vp, vp, vp, vp, vp, C.POINTER(Epilogue), vp]
+    L.gz_gemm_run_ex.restype = C.c_int
     L.gz_gemm_plan_set_profile.argtypes = [vp, vp]
     L.gz_gemm_plan_set_profile.restype = C.c_int
     L.gz_gemm_run_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp]
@@ -155,8 +174,10 @@ def partition_columns(n, parts, p, align=8):
     return b.value, e.value
 
 
-def _scalar(in_type, v):
-    return C.c_int32(int(v)) if in_type == DT_S8 else C.c_float(float(v))
+def _scalar(in_type, v, out_type=None):
+    """alpha / beta in the type the C ABI reads: int32 for s32 outputs, float otherwise."""
+    is_int = (out_type == DT_S32) if out_type is not None else (in_type == DT_S8)
+    return C.c_int32(int(v)) if is_int else C.c_float(float(v))
 
 
 def _ptr(x):
@@ -199,14 +220,27 @@ class Plan:
         return info
 
     def run(self, a, b, c, d, alpha, beta, stream=None):
-        al, be = _scalar(self.desc.in_type, alpha), _scalar(self.desc.in_type, beta)
+        al, be = (_scalar(self.desc.in_type, alpha, self.desc.out_type),
+                  _scalar(self.desc.in_type, beta, self.desc.out_type))
         st = lib().gz_gemm_run(self._h, _ptr(a), _ptr(b), _ptr(c), _ptr(d), C.byref(al), C.byref(be),
                                _stream_handle(stream))
         if st != GZ_OK:
             raise GzError(st, "gz_gemm_run")
 
+    def run_ex(self, a, b, c, d, alpha, beta, bias=None, row_scale=None, col_scale=None, activation=ACT_NONE,
+               stream=None):
+        """gz_gemm_run_ex: bias / row_scale / col_scale are fp32 device vectors (or None)."""
+        al, be = (_scalar(self.desc.in_type, alpha, self.desc.out_type),
+                  _scalar(self.desc.in_type, beta, self.desc.out_type))
+        ep = Epilogue.make(bias, row_scale, col_scale, activation)
+        st = lib().gz_gemm_run_ex(self._h, _ptr(a), _ptr(b), _ptr(c), _ptr(d), C.byref(al), C.byref(be),
+                                  C.byref(ep), _stream_handle(stream))
+        if st != GZ_OK:
+            raise GzError(st, "gz_gemm_run_ex")
+
     def run_host(self, a, b, c, d, alpha, beta, stream=None):
-        al, be = _scalar(self.desc.in_type, alpha), _scalar(self.desc.in_type, beta)
+        al, be = (_scalar(self.desc.in_type, alpha, self.desc.out_type),
+                  _scalar(self.desc.in_type, beta, self.desc.out_type))
         st = lib().gz_gemm_run_host(self._h, _ptr(a), _ptr(b), _ptr(c), _ptr(d), C.byref(al),
                                     C.byref(be), _stream_handle(stream))
         if st != GZ_OK:

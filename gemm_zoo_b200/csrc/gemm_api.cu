@@ -99,6 +99,8 @@ bool pair_supported(int in, int out) {
   return (in == GZ_DT_F16 && (out == GZ_DT_F16 || out == GZ_DT_F32)) ||
          (in == GZ_DT_BF16 && (out == GZ_DT_BF16 || out == GZ_DT_F32)) ||
          (in == GZ_DT_F32 && out == GZ_DT_F32) || (in == GZ_DT_S8 && out == GZ_DT_S32) ||
+         // int32 accumulation, float epilogue (dequantising GEMM)
+         (in == GZ_DT_S8 && (out == GZ_DT_F16 || out == GZ_DT_BF16 || out == GZ_DT_F32)) ||
          (is_fp8(in) && (out == GZ_DT_F16 || out == GZ_DT_BF16 || out == GZ_DT_F32));
 }
 
@@ -265,7 +267,7 @@ int choose_config(const Problem& pr, int sm_count) {
     // Clocks per tile during which the tensor pipe waits for the epilogue: only the accumulator
     // hand-over when a warp's share of both accumulators fits its registers (16-bit outputs),
     // most of the output stores otherwise.
-    const double per_tile = s.mb == 2 ? (pr.out_size == 2 ? 3500.0 : 12000.0) : 0.0;
+    const double per_tile = s.mb == 2 ? (pr.out_size == 2 ? 3500.0 : 6000.0) : 0.0;
     double blocks_per_cta;
     if (wants_split_k(pr, s, sm_count)) {
       const int64_t total = tiles * k_blocks;
@@ -440,7 +442,10 @@ KernelEntry entry_for(int in, int out, int config) {
   if ((in == GZ_DT_F16 || in == GZ_DT_BF16) && out == GZ_DT_F32)
     return entry_for_shape<Kind::F16, float>(config);
   if (in == GZ_DT_F32) return entry_for_shape<Kind::TF32, float>(config);
-  if (in == GZ_DT_S8) return entry_for_shape<Kind::I8, int32_t>(config);
+  if (in == GZ_DT_S8 && out == GZ_DT_S32) return entry_for_shape<Kind::I8, int32_t>(config);
+  if (in == GZ_DT_S8 && out == GZ_DT_F16) return entry_for_shape<Kind::I8, __half>(config);
+  if (in == GZ_DT_S8 && out == GZ_DT_BF16) return entry_for_shape<Kind::I8, __nv_bfloat16>(config);
+  if (in == GZ_DT_S8 && out == GZ_DT_F32) return entry_for_shape<Kind::I8, float>(config);
   if (is_fp8(in) && out == GZ_DT_F16) return entry_for_shape<Kind::F8, __half>(config);
   if (is_fp8(in) && out == GZ_DT_BF16) return entry_for_shape<Kind::F8, __nv_bfloat16>(config);
   if (is_fp8(in) && out == GZ_DT_F32) return entry_for_shape<Kind::F8, float>(config);
@@ -461,7 +466,10 @@ cudaError_t launch_simt_any(int in, int out, const gz::SimtParams& sp, cudaStrea
     return launch_simt<__nv_bfloat16, __nv_bfloat16>(sp, stream);
   if (in == GZ_DT_BF16 && out == GZ_DT_F32) return launch_simt<__nv_bfloat16, float>(sp, stream);
   if (in == GZ_DT_F32) return launch_simt<float, float>(sp, stream);
-  if (in == GZ_DT_S8) return launch_simt<int8_t, int32_t>(sp, stream);
+  if (in == GZ_DT_S8 && out == GZ_DT_S32) return launch_simt<int8_t, int32_t>(sp, stream);
+  if (in == GZ_DT_S8 && out == GZ_DT_F16) return launch_simt<int8_t, __half>(sp, stream);
+  if (in == GZ_DT_S8 && out == GZ_DT_BF16) return launch_simt<int8_t, __nv_bfloat16>(sp, stream);
+  if (in == GZ_DT_S8 && out == GZ_DT_F32) return launch_simt<int8_t, float>(sp, stream);
   if (in == GZ_DT_E4M3 && out == GZ_DT_F16) return launch_simt<__nv_fp8_e4m3, __half>(sp, stream);
   if (in == GZ_DT_E4M3 && out == GZ_DT_BF16) return launch_simt<__nv_fp8_e4m3, __nv_bfloat16>(sp, stream);
   if (in == GZ_DT_E4M3 && out == GZ_DT_F32) return launch_simt<__nv_fp8_e4m3, float>(sp, stream);
@@ -594,7 +602,7 @@ gz_status read_scalars(const Problem& pr, const void* alpha, const void* beta, f
   if (!alpha || !beta) return GZ_ERR_INVALID_ARG;
   *af = *bf = 0.f;
   *ai = *bi = 0;
-  if (pr.d.in_type == GZ_DT_S8) {
+  if (pr.d.out_type == GZ_DT_S32) {
     *ai = *static_cast<const int32_t*>(alpha);
     *bi = *static_cast<const int32_t*>(beta);
   } else {
@@ -843,9 +851,19 @@ struct ScatterSpec {
 };
 
 gz_status run_impl(gz_plan* pl, const void* a, const void* b, const void* c, void* d, const void* alpha,
-                   const void* beta, void* stream_v, const ScatterSpec* sc) {
+                   const void* beta, void* stream_v, const ScatterSpec* sc, const gz_epilogue* ep = nullptr) {
   if (!pl || !a || !b || !d) return GZ_ERR_INVALID_ARG;
   const Problem& pr = pl->pr;
+  uint32_t epi_flags = 0;
+  if (ep) {
+    if (ep->struct_size != sizeof(gz_epilogue) || ep->activation < GZ_ACT_NONE || ep->activation > GZ_ACT_SILU)
+      return GZ_ERR_INVALID_ARG;
+    epi_flags = (ep->bias ? 1u : 0u) | (ep->row_scale ? 2u : 0u) | (ep->col_scale ? 4u : 0u) |
+                (ep->activation != GZ_ACT_NONE ? 8u : 0u);
+    if (epi_flags != 0 && pr.d.out_type == GZ_DT_S32) return GZ_ERR_UNSUPPORTED;
+    auto bad = [](const float* q) { return q && reinterpret_cast<uintptr_t>(q) % 4 != 0; };
+    if (bad(ep->bias) || bad(ep->row_scale) || bad(ep->col_scale)) return GZ_ERR_MISALIGNED;
+  }
   if (sc) {
     if (pl->info.config == GZ_CFG_SIMT || pr.out_size != 4 || sc->cols == 0 || sc->cols % 32 != 0 ||
         sc->parts < 1 || sc->parts > 8 || (int64_t)sc->cols * sc->parts < pr.d.n || sc->ld < sc->cols)
@@ -855,7 +873,7 @@ gz_status run_impl(gz_plan* pl, const void* a, const void* b, const void* c, voi
   int32_t ai, bi;
   gz_status st = read_scalars(pr, alpha, beta, &af, &bf, &ai, &bi);
   if (st != GZ_OK) return st;
-  const bool beta_zero = (pr.d.in_type == GZ_DT_S8) ? (bi == 0) : (bf == 0.0f);
+  const bool beta_zero = (pr.d.out_type == GZ_DT_S32) ? (bi == 0) : (bf == 0.0f);
   if (!beta_zero && !c) return GZ_ERR_INVALID_ARG;
   auto misaligned = [](const void* p, int sz) { return (reinterpret_cast<uintptr_t>(p) % sz) != 0; };
   if (misaligned(a, pr.in_size) || misaligned(b, pr.in_size) || misaligned(d, pr.out_size) ||
@@ -887,6 +905,11 @@ gz_status run_impl(gz_plan* pl, const void* a, const void* b, const void* c, voi
     sp.beta_f = bf;
     sp.alpha_i = ai;
     sp.beta_i = bi;
+    sp.epi_flags = epi_flags;
+    sp.act = epi_flags ? (uint32_t)ep->activation : 0u;
+    sp.bias = epi_flags ? ep->bias : nullptr;
+    sp.row_scale = epi_flags ? ep->row_scale : nullptr;
+    sp.col_scale = epi_flags ? ep->col_scale : nullptr;
     if (!cuda_ok(launch_simt_any(pr.d.in_type, pr.d.out_type, sp, stream), "simt launch"))
       return GZ_ERR_CUDA;
     return GZ_OK;
@@ -903,6 +926,15 @@ gz_status run_impl(gz_plan* pl, const void* a, const void* b, const void* c, voi
   p.c_vec_ok = (c && reinterpret_cast<uintptr_t>(c) % 16 == 0 && (pr.d.ldc * pr.out_size) % 16 == 0) ? 1u : 0u;
   p.d_vec_ok = (reinterpret_cast<uintptr_t>(d) % 16 == 0 && (pr.d.ldd * pr.out_size) % 16 == 0) ? 1u : 0u;
   if (p.epilogue_tma && reinterpret_cast<uintptr_t>(d) % 16 != 0) p.epilogue_tma = 0;
+  if (epi_flags) {
+    p.epi_flags = epi_flags;
+    p.act = (uint32_t)ep->activation;
+    // The swapped (skinny) tiles walk N along the 128-row side; the kernel indexes the vectors by
+    // output row and column, so nothing is exchanged here.
+    p.bias = ep->bias;
+    p.row_scale = ep->row_scale;
+    p.col_scale = ep->col_scale;
+  }
   if (sc) {
     p.epilogue_tma = 0;
     p.scatter_cols = sc->cols;
@@ -957,6 +989,11 @@ GZ_API gz_status gz_gemm_run(gz_plan* pl, const void* a, const void* b, const vo
   return run_impl(pl, a, b, c, d, alpha, beta, stream_v, nullptr);
 }
 
+GZ_API gz_status gz_gemm_run_ex(gz_plan* pl, const void* a, const void* b, const void* c, void* d,
+                                const void* alpha, const void* beta, const gz_epilogue* ep, void* stream_v) {
+  return run_impl(pl, a, b, c, d, alpha, beta, stream_v, nullptr, ep);
+}
+
 GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, const void* c, void* d,
                                   const void* alpha, const void* beta, void* stream_v) {
   if (!pl || !a || !b || !d) return GZ_ERR_INVALID_ARG;
@@ -965,7 +1002,7 @@ GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, con
   int32_t ai, bi;
   gz_status st = read_scalars(pr, alpha, beta, &af, &bf, &ai, &bi);
   if (st != GZ_OK) return st;
-  const bool beta_zero = (pr.d.in_type == GZ_DT_S8) ? (bi == 0) : (bf == 0.0f);
+  const bool beta_zero = (pr.d.out_type == GZ_DT_S32) ? (bi == 0) : (bf == 0.0f);
   if (!beta_zero && !c) return GZ_ERR_INVALID_ARG;
   DeviceGuard guard(pr.d.device);
   if (!guard.ok()) return GZ_ERR_CUDA;
@@ -1282,7 +1319,7 @@ extern "C" GZ_API gz_status gz_gemm_skinny_static(const gz_gemm_desc* desc, cons
   int32_t ai, bi;
   st = read_scalars(pr, alpha, beta, &af, &bf, &ai, &bi);
   if (st != GZ_OK) return st;
-  const bool beta_zero = (pr.d.in_type == GZ_DT_S8) ? (bi == 0) : (bf == 0.0f);
+  const bool beta_zero = (pr.d.out_type == GZ_DT_S32) ? (bi == 0) : (bf == 0.0f);
   if (!beta_zero && !c) return GZ_ERR_INVALID_ARG;
 
   StaticScratchDevice* sd = nullptr;

@@ -238,6 +238,7 @@ GZ_API gz_status gz_ks_plan_create(gz_ks_plan** out, const gz_ks_desc* desc, voi
     if (!workspaces[g] || reinterpret_cast<uintptr_t>(workspaces[g]) % 256 != 0) return GZ_ERR_INVALID_ARG;
   const bool s8 = desc->in_type == GZ_DT_S8;
   if (!pair_supported(desc->in_type, desc->out_type)) return GZ_ERR_UNSUPPORTED;
+  if (s8 && desc->out_type != GZ_DT_S32) return GZ_ERR_UNSUPPORTED;  // int32 slots are added as integers
 
   gz_gemm_desc gd;
   std::memset(&gd, 0, sizeof(gd));

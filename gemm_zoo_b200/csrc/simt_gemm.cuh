@@ -29,6 +29,11 @@ struct SimtParams {
   int64_t ldc, ldd;
   float alpha_f, beta_f;
   int32_t alpha_i, beta_i;
+  // optional epilogue terms (float outputs): D = act(alpha * rs[i] * cs[j] * acc + beta * C + bias[j])
+  uint32_t epi_flags, act;
+  const float* bias;
+  const float* row_scale;
+  const float* col_scale;
 };
 
 namespace detail {
@@ -63,6 +68,18 @@ __device__ __forceinline__ __half simt_from_f<__half>(float v) {
 template <>
 __device__ __forceinline__ __nv_bfloat16 simt_from_f<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ float simt_activate(float x, uint32_t act) {
+  switch (act) {
+    case 1: return fmaxf(x, 0.0f);
+    case 2: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    case 3: {
+      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.0f + tanhf(u));
+    }
+    case 4: return x / (1.0f + __expf(-x));
+    default: return x;
+  }
 }
 }  // namespace detail
 
@@ -137,14 +154,22 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
     for (int j = 0; j < 4; ++j) {
       const int64_t gn = n0 + tx * 4 + j;
       if (gn >= p.n) continue;
-      if constexpr (INT) {
+      if constexpr (std::is_same<TOut, int32_t>::value) {
         uint32_t v = static_cast<uint32_t>(p.alpha_i) * static_cast<uint32_t>(acc[i][j]);
         if (p.beta_i != 0)
           v += static_cast<uint32_t>(p.beta_i) * static_cast<uint32_t>(c[gm * p.ldc + gn]);
         d[gm * p.ldd + gn] = static_cast<int32_t>(v);
       } else {
-        float v = p.alpha_f * acc[i][j];
+        float v = p.alpha_f * static_cast<float>(acc[i][j]);
+        if (p.epi_flags) {
+          if (p.row_scale) v *= p.row_scale[gm];
+          if (p.col_scale) v *= p.col_scale[gn];
+        }
         if (p.beta_f != 0.0f) v = fmaf(p.beta_f, detail::simt_to_f(c[gm * p.ldc + gn]), v);
+        if (p.epi_flags) {
+          if (p.bias) v += p.bias[gn];
+          v = detail::simt_activate(v, p.act);
+        }
         d[gm * p.ldd + gn] = detail::simt_from_f<TOut>(v);
       }
     }

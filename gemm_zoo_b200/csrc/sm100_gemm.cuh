@@ -114,6 +114,15 @@ struct GemmParams {
   // partial sums straight to the GPU that owns the block.  Direct-store epilogue only.
   uint32_t scatter_cols;
   void* scatter_ptrs[8];
+  // Optional epilogue terms (floating-point outputs only), applied in fp32:
+  //   D = act(alpha * row_scale[i] * col_scale[j] * acc + beta * C + bias[j])
+  // epi_flags != 0 says that at least one of them is present (bit 0 bias, 1 row_scale,
+  // 2 col_scale, 3 activation); the kernel then takes its slice-by-slice epilogue.
+  uint32_t epi_flags;
+  uint32_t act;  // 0 none, 1 relu, 2 gelu (erf), 3 gelu (tanh), 4 silu
+  const float* bias;
+  const float* row_scale;
+  const float* col_scale;
   // Tuning switches (see TUNE_* below).
   uint32_t tune;
   // Optional stall counters, 16 words per CTA (null = off):
@@ -325,13 +334,47 @@ __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
   return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
 }
 
+// An accumulator word as fp32: int32 accumulators (kind::i8) are converted, the rest reinterpreted.
+template <bool ACC_INT>
+__device__ __forceinline__ float acc_as_float(uint32_t v) {
+  if constexpr (ACC_INT) return static_cast<float>(static_cast<int32_t>(v));
+  else return __uint_as_float(v);
+}
+
+__device__ __forceinline__ float activate(float x, uint32_t act) {
+  switch (act) {
+    case 1: return fmaxf(x, 0.0f);
+    case 2: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    case 3: {
+      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.0f + tanhf(u));
+    }
+    case 4: return x / (1.0f + __expf(-x));
+    default: return x;
+  }
+}
+
+// The optional terms around one element: epi_scale() takes alpha * acc, epi_finish() takes
+// alpha * rs * cs * acc + beta * c.
+__device__ __forceinline__ float epi_scale(const GemmParams& p, float f, uint32_t row, uint32_t col) {
+  if (p.row_scale) f *= __ldg(p.row_scale + row);
+  if (p.col_scale) f *= __ldg(p.col_scale + col);
+  return f;
+}
+__device__ __forceinline__ float epi_finish(const GemmParams& p, float f, uint32_t col) {
+  if (p.bias) f += __ldg(p.bias + col);
+  return activate(f, p.act);
+}
+
 // alpha * acc + beta * c for one 32-column slice of one row.
 //   v[32]     in:  raw accumulator words;  out: packed output words (32 * sizeof(TOut) / 4 used)
 //   crow      pointer to C(row, col0) (only dereferenced when beta != 0 and row_ok)
 //   ncols     valid columns in this slice (1..32)
-template <typename TOut>
+//   row, col0 output coordinates of the slice (for the optional per-row / per-column terms)
+template <typename TOut, bool ACC_INT>
 __device__ __forceinline__ void epilogue_math(uint32_t (&v)[32], const GemmParams& p,
-                                              const TOut* crow, bool row_ok, uint32_t ncols) {
+                                              const TOut* crow, bool row_ok, uint32_t ncols,
+                                              uint32_t row, uint32_t col0) {
   using Tr = OutTraits<TOut>;
   if constexpr (Tr::INT) {
     const uint32_t alpha = static_cast<uint32_t>(p.alpha_i);
@@ -363,7 +406,12 @@ __device__ __forceinline__ void epilogue_math(uint32_t (&v)[32], const GemmParam
     const float beta = p.beta_f;
     float f[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) f[i] = alpha * __uint_as_float(v[i]);
+    for (int i = 0; i < 32; ++i) f[i] = alpha * acc_as_float<ACC_INT>(v[i]);
+    if (p.epi_flags != 0u && row_ok) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (static_cast<uint32_t>(i) < ncols) f[i] = epi_scale(p, f[i], row, col0 + i);
+    }
     if (beta != 0.0f && row_ok) {
       if (ncols == 32 && p.c_vec_ok) {
         constexpr int PER16 = 16 / sizeof(TOut);  // elements per 16-byte load
@@ -382,6 +430,11 @@ __device__ __forceinline__ void epilogue_math(uint32_t (&v)[32], const GemmParam
           if (static_cast<uint32_t>(i) < ncols) f[i] = fmaf(beta, Tr::to_f(crow[i]), f[i]);
       }
     }
+    if (p.epi_flags != 0u && row_ok) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (static_cast<uint32_t>(i) < ncols) f[i] = epi_finish(p, f[i], col0 + i);
+    }
     if constexpr (sizeof(TOut) == 4) {
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(f[i]);
@@ -393,16 +446,19 @@ __device__ __forceinline__ void epilogue_math(uint32_t (&v)[32], const GemmParam
 }
 
 // alpha * acc (+ beta * *c) for a single element (the swapped-operand epilogue).
-template <typename TOut, bool HAS_BETA>
-__device__ __forceinline__ TOut epilogue_scalar(uint32_t acc, const GemmParams& p, const TOut* c) {
+template <typename TOut, bool HAS_BETA, bool ACC_INT>
+__device__ __forceinline__ TOut epilogue_scalar(uint32_t acc, const GemmParams& p, const TOut* c, uint32_t row,
+                                                uint32_t col) {
   using Tr = OutTraits<TOut>;
   if constexpr (Tr::INT) {
     uint32_t v = static_cast<uint32_t>(p.alpha_i) * acc;
     if constexpr (HAS_BETA) v += static_cast<uint32_t>(p.beta_i) * static_cast<uint32_t>(*c);
     return static_cast<int32_t>(v);
   } else {
-    float f = p.alpha_f * __uint_as_float(acc);
+    float f = p.alpha_f * acc_as_float<ACC_INT>(acc);
+    if (p.epi_flags != 0u) f = epi_scale(p, f, row, col);
     if constexpr (HAS_BETA) f = fmaf(p.beta_f, Tr::to_f(*c), f);
+    if (p.epi_flags != 0u) f = epi_finish(p, f, col);
     if constexpr (sizeof(TOut) == 4) return f;
     else if constexpr (std::is_same<TOut, __half>::value) return __float2half_rn(f);
     else return __float2bfloat16_rn(f);
@@ -471,7 +527,7 @@ __device__ __forceinline__ void store_staged_box(const GemmParams& p, uint32_t s
 // alpha * acc (+ beta * c) for one full 32-column slice of one row, in place and without a second
 // register array: on return x[0 .. 32 * sizeof(TOut) / 4) holds the packed outputs.  `crow` points
 // at C(row, col0), 16-byte aligned; it is read only when HAS_BETA.
-template <typename TOut, bool HAS_BETA>
+template <typename TOut, bool HAS_BETA, bool ACC_INT>
 __device__ __forceinline__ void scale_slice_in_place(uint32_t (&x)[32], const GemmParams& p, const TOut* crow) {
   using Tr = OutTraits<TOut>;
   const uint4* c4 = reinterpret_cast<const uint4*>(crow);
@@ -491,8 +547,8 @@ __device__ __forceinline__ void scale_slice_in_place(uint32_t (&x)[32], const Ge
     const float alpha = p.alpha_f, beta = p.beta_f;
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      float f0 = alpha * __uint_as_float(x[4 * q + 0]), f1 = alpha * __uint_as_float(x[4 * q + 1]);
-      float f2 = alpha * __uint_as_float(x[4 * q + 2]), f3 = alpha * __uint_as_float(x[4 * q + 3]);
+      float f0 = alpha * acc_as_float<ACC_INT>(x[4 * q + 0]), f1 = alpha * acc_as_float<ACC_INT>(x[4 * q + 1]);
+      float f2 = alpha * acc_as_float<ACC_INT>(x[4 * q + 2]), f3 = alpha * acc_as_float<ACC_INT>(x[4 * q + 3]);
       if constexpr (HAS_BETA) {
         const uint4 cv = c4[q];
         f0 = fmaf(beta, __uint_as_float(cv.x), f0);
@@ -516,8 +572,8 @@ __device__ __forceinline__ void scale_slice_in_place(uint32_t (&x)[32], const Ge
       const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        float lo = alpha * __uint_as_float(x[8 * q + 2 * e]);
-        float hi = alpha * __uint_as_float(x[8 * q + 2 * e + 1]);
+        float lo = alpha * acc_as_float<ACC_INT>(x[8 * q + 2 * e]);
+        float hi = alpha * acc_as_float<ACC_INT>(x[8 * q + 2 * e + 1]);
         if constexpr (HAS_BETA) {
           const float2 cf = unpack2<TOut>(cw[e]);
           lo = fmaf(beta, cf.x, lo);
@@ -536,6 +592,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1)
 sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_d, const GemmParams p) {
   using TOut = typename Cfg::TOut;
+  constexpr bool ACC_INT = Cfg::KIND == ptx::Kind::I8;  // int32 accumulators
   constexpr int CTAS = Cfg::CTAS;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int BN = Cfg::BN;
@@ -901,7 +958,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           // before a single byte is stored; the stores then drain under the next main loop.
           // (All CTAs finish their tiles at about the same time, so the burst of output stores
           // is slow to drain; it must not hold up tensor memory.)
-          const bool plain = detail::OutTraits<TOut>::INT ? false : (p.beta_f == 0.0f);
+          const bool plain = detail::OutTraits<TOut>::INT ? false : (p.beta_f == 0.0f && p.epi_flags == 0u);
           if (plain && wcols == static_cast<uint32_t>(WARP_COLS) && col_w + WARP_COLS <= p.n &&
               (p.epilogue_tma || p.d_vec_ok)) {
             uint32_t y[2][NSL][16];
@@ -928,7 +985,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               }
 #pragma unroll
               for (int sl = 0; sl < NSL; ++sl) {
-                detail::scale_slice_in_place<TOut, false>(v[sl], p, nullptr);
+                detail::scale_slice_in_place<TOut, false, ACC_INT>(v[sl], p, nullptr);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) y[0][sl][i] = v[sl][i];
               }
@@ -943,7 +1000,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               uint32_t x[32];
               ptx::tmem_ld_32x32(taddr0 + BN + sl * 32u, x);
               ptx::tmem_wait_ld();
-              detail::scale_slice_in_place<TOut, false>(x, p, nullptr);
+              detail::scale_slice_in_place<TOut, false, ACC_INT>(x, p, nullptr);
 #pragma unroll
               for (int i = 0; i < 16; ++i) y[1][sl][i] = x[i];
             }
@@ -1015,7 +1072,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           // accessed in 16-byte vectors.  Everything else (edge tiles, tail strips, unaligned
           // operands) takes the slice-by-slice path below, which frees the accumulator last.
           const bool fast = wcols == static_cast<uint32_t>(WARP_COLS) && col_w + WARP_COLS <= p.n &&
-                            (p.epilogue_tma || p.d_vec_ok) && (!has_beta || p.c_vec_ok);
+                            (p.epilogue_tma || p.d_vec_ok) && (!has_beta || p.c_vec_ok) && p.epi_flags == 0u;
           if (fast) {
             uint32_t v[NSL][32];
 #pragma unroll
@@ -1043,9 +1100,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   uint32_t(&x)[32] = v[box * SLICES + sl];
                   const int c_off = box * BOX_COLS + sl * 32;
                   if (has_beta) {
-                    if (row_ok) detail::scale_slice_in_place<TOut, true>(x, p, crow + c_off);
+                    if (row_ok) detail::scale_slice_in_place<TOut, true, ACC_INT>(x, p, crow + c_off);
                   } else {
-                    detail::scale_slice_in_place<TOut, false>(x, p, nullptr);
+                    detail::scale_slice_in_place<TOut, false, ACC_INT>(x, p, nullptr);
                   }
 #pragma unroll
                   for (int q = 0; q < WORDS / 4; ++q) {
@@ -1089,7 +1146,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   ptx::tmem_ld_32x32(taddr + box * BOX_COLS + sl * 32u, x);
                   ptx::tmem_wait_ld();
                   const TOut* crow = cmat + static_cast<int64_t>(row) * p.ldc + col0;
-                  detail::epilogue_math<TOut>(x, p, crow, row_ok, ncols);
+                  detail::epilogue_math<TOut, ACC_INT>(x, p, crow, row_ok, ncols, row, col0);
                   if (p.epilogue_tma) {
 #pragma unroll
                     for (int q = 0; q < WORDS / 4; ++q) {
@@ -1245,7 +1302,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   for (int q = 0; q < 4; ++q) {
                     if (c0 + cc == 0u) {
                       sum[q] = x[cc][q];
-                    } else if constexpr (detail::OutTraits<TOut>::INT) {
+                    } else if constexpr (ACC_INT) {
                       sum[q].x = __uint_as_float(__float_as_uint(sum[q].x) + __float_as_uint(x[cc][q].x));
                       sum[q].y = __uint_as_float(__float_as_uint(sum[q].y) + __float_as_uint(x[cc][q].y));
                       sum[q].z = __uint_as_float(__float_as_uint(sum[q].z) + __float_as_uint(x[cc][q].z));
@@ -1278,12 +1335,14 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 for (int i = 0; i < 16; ++i)
                   if (static_cast<uint32_t>(i) < cnt)
                     dp[static_cast<int64_t>(i) * p.ldd] =
-                        detail::epilogue_scalar<TOut, true>(v[i], p, cp + static_cast<int64_t>(i) * p.ldc);
+                        detail::epilogue_scalar<TOut, true, ACC_INT>(v[i], p, cp + static_cast<int64_t>(i) * p.ldc,
+                                                                     mrow0 + i, ncol);
               } else {
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
                   if (static_cast<uint32_t>(i) < cnt)
-                    dp[static_cast<int64_t>(i) * p.ldd] = detail::epilogue_scalar<TOut, false>(v[i], p, nullptr);
+                    dp[static_cast<int64_t>(i) * p.ldd] =
+                        detail::epilogue_scalar<TOut, false, ACC_INT>(v[i], p, nullptr, mrow0 + i, ncol);
               }
             }
           }

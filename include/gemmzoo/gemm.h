@@ -26,7 +26,7 @@
  *     Reference default: A row-major lda=K, B row-major ldb=N, C/D ld=N
  *     (nvidia/kernels/naive_gemm.cuh:18-20).
  *   - alpha and beta are passed by HOST pointer in the scale type of the
- *     problem: float for f16/bf16/f32/fp8 inputs, int32_t for s8 inputs.
+ *     problem: int32_t when the output type is s32, float otherwise.
  *   - C is not read when beta == 0 (the rule of nvidia/kernels/generic_gemm.cuh:55).
  *     D may alias C.
  *   - Nothing here exits the process or throws; every entry point returns a
@@ -164,6 +164,35 @@ GZ_API gz_status gz_gemm_plan_set_profile(gz_plan* plan, void* device_words);
  * a, b, c, d: device pointers.  c may be NULL when *beta == 0. */
 GZ_API gz_status gz_gemm_run(gz_plan* plan, const void* a, const void* b, const void* c, void* d,
                              const void* alpha, const void* beta, void* stream);
+
+/* Optional epilogue terms for floating-point outputs, applied in fp32 inside the GEMM's epilogue:
+ *
+ *     D[i][j] = act(alpha * row_scale[i] * col_scale[j] * acc[i][j] + beta * C[i][j] + bias[j])
+ *
+ * Any pointer may be NULL (term absent).  With s8 inputs and an f16/bf16/f32 output type this is
+ * the dequantising GEMM (int32 accumulation, per-row and per-column scales).  No counterpart in the
+ * reference's own kernels; the nearest thing is the bias its Intel test passes to the library
+ * (intel/test/utils.hpp:133-136). */
+typedef enum gz_activation {
+  GZ_ACT_NONE = 0,
+  GZ_ACT_RELU = 1,
+  GZ_ACT_GELU = 2,      /* 0.5 x (1 + erf(x / sqrt 2)) */
+  GZ_ACT_GELU_TANH = 3, /* 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) */
+  GZ_ACT_SILU = 4       /* x / (1 + exp(-x)) */
+} gz_activation;
+
+typedef struct gz_epilogue {
+  uint32_t struct_size; /* sizeof(gz_epilogue) */
+  int32_t activation;   /* gz_activation */
+  const float* bias;      /* n floats on the device, or NULL */
+  const float* row_scale; /* m floats on the device, or NULL */
+  const float* col_scale; /* n floats on the device, or NULL */
+} gz_epilogue;
+
+/* gz_gemm_run with the optional terms (ep may be NULL: identical to gz_gemm_run).
+ * GZ_ERR_UNSUPPORTED for plans with an s32 output. */
+GZ_API gz_status gz_gemm_run_ex(gz_plan* plan, const void* a, const void* b, const void* c, void* d,
+                                const void* alpha, const void* beta, const gz_epilogue* ep, void* stream);
 
 /* Same computation with HOST operands: copies A, B (and C when beta != 0) to
  * device staging owned by the plan, runs, copies D back, and synchronises the

@@ -171,3 +171,41 @@ def round_to(out_type, x: np.ndarray):
     if out_type == DT_F32:
         return t.to(torch.float32)
     raise ValueError(out_type)
+
+
+ACT_NONE, ACT_RELU, ACT_GELU, ACT_GELU_TANH, ACT_SILU = 0, 1, 2, 3, 4
+
+
+def activate_f64(x: np.ndarray, act: int) -> np.ndarray:
+    """The activations of gz_activation (include/gemmzoo/gemm.h) in double."""
+    import math
+    if act == ACT_NONE:
+        return x
+    if act == ACT_RELU:
+        return np.maximum(x, 0.0)
+    if act == ACT_GELU:
+        erf = np.vectorize(math.erf, otypes=[np.float64])
+        return 0.5 * x * (1.0 + erf(x / math.sqrt(2.0)))
+    if act == ACT_GELU_TANH:
+        return 0.5 * x * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * x ** 3)))
+    if act == ACT_SILU:
+        return x / (1.0 + np.exp(-x))
+    raise ValueError(act)
+
+
+def epilogue_f64(acc, c, alpha, beta, bias=None, row_scale=None, col_scale=None, act=ACT_NONE) -> np.ndarray:
+    """act(alpha * row_scale[i] * col_scale[j] * acc + beta * C + bias[j]) in double.
+
+    `acc` is the unscaled product A*B (gemm_f64 / gemm_s8 with alpha=1, beta=0).  The reference's
+    kernels stop at alpha/beta (nvidia/kernels/generic_gemm.cuh:53-58); the extra terms follow the
+    definition in include/gemmzoo/gemm.h (gz_epilogue)."""
+    r = float(alpha) * np.asarray(acc, dtype=np.float64)
+    if row_scale is not None:
+        r = r * np.asarray(row_scale, dtype=np.float64)[:, None]
+    if col_scale is not None:
+        r = r * np.asarray(col_scale, dtype=np.float64)[None, :]
+    if c is not None and beta != 0:
+        r = r + float(beta) * np.asarray(c, dtype=np.float64)
+    if bias is not None:
+        r = r + np.asarray(bias, dtype=np.float64)[None, :]
+    return activate_f64(r, act)

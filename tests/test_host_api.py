@@ -85,7 +85,7 @@ def test_validate_ok_and_defaults():
     (dict(flags=gz.FLAG_EPILOGUE_DIRECT | gz.FLAG_EPILOGUE_TMA), api.GZ_ERR_INVALID_ARG),
     (dict(flags=0x100), api.GZ_ERR_INVALID_ARG),
     (dict(in_type=gz.DT_BF16, out_type=gz.DT_F16), api.GZ_ERR_UNSUPPORTED),
-    (dict(in_type=gz.DT_S8, out_type=gz.DT_F32), api.GZ_ERR_UNSUPPORTED),
+    (dict(in_type=gz.DT_F32, out_type=gz.DT_BF16), api.GZ_ERR_UNSUPPORTED),
     (dict(in_type=gz.DT_S32, out_type=gz.DT_S32), api.GZ_ERR_UNSUPPORTED),
     (dict(m=2 ** 31), api.GZ_ERR_TOO_LARGE),
     (dict(k=2 ** 33), api.GZ_ERR_TOO_LARGE),
