@@ -17,6 +17,7 @@ CFG_SWAP_M16, CFG_SWAP_M32, CFG_SWAP_M64, CFG_SWAP_M128 = 6, 7, 8, 9
 CFG_2CTA_M512_N256 = 10
 FLAG_EPILOGUE_DIRECT, FLAG_EPILOGUE_TMA, FLAG_TEST_WITHHOLD_ACC_READY = 0x1, 0x2, 0x80000000
 FLAG_NO_SPLIT_K, FLAG_SPLIT_K = 0x4, 0x8
+FLAG_BROADCAST_A, FLAG_BROADCAST_B = 0x10, 0x20
 
 GZ_OK = 0
 GZ_ERR_INVALID_ARG, GZ_ERR_UNSUPPORTED, GZ_ERR_MISALIGNED, GZ_ERR_CUDA = 1, 2, 3, 4
@@ -56,11 +57,14 @@ class GemmDesc(C.Structure):
         ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
         ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64), ("ldd", C.c_int64),
         ("wait_limit_ns", C.c_uint64),
+        ("batch", C.c_int64), ("stride_a", C.c_int64), ("stride_b", C.c_int64), ("stride_c", C.c_int64),
+        ("stride_d", C.c_int64),
     ]
 
     @classmethod
     def make(cls, in_type, out_type, m, n, k, layout_a=ROW_MAJOR, layout_b=ROW_MAJOR, lda=0, ldb=0,
-             ldc=0, ldd=0, device=0, config=CFG_AUTO, flags=0, wait_limit_ns=0):
+             ldc=0, ldd=0, device=0, config=CFG_AUTO, flags=0, wait_limit_ns=0, batch=1, stride_a=0,
+             stride_b=0, stride_c=0, stride_d=0):
         d = cls()
         d.struct_size = C.sizeof(cls)
         d.in_type, d.out_type = in_type, out_type
@@ -69,6 +73,7 @@ class GemmDesc(C.Structure):
         d.m, d.n, d.k = m, n, k
         d.lda, d.ldb, d.ldc, d.ldd = lda, ldb, ldc, ldd
         d.wait_limit_ns = wait_limit_ns
+        d.batch, d.stride_a, d.stride_b, d.stride_c, d.stride_d = batch, stride_a, stride_b, stride_c, stride_d
         return d
 
 
@@ -292,11 +297,12 @@ class Sm100Gemm:
     """
 
     def __init__(self, m, n, k, in_dtype, out_dtype, layout_a=ROW_MAJOR, layout_b=ROW_MAJOR, lda=0,
-                 ldb=0, ldc=0, ldd=0, device=0, config=CFG_AUTO, flags=0, wait_limit_ns=0):
+                 ldb=0, ldc=0, ldd=0, device=0, config=CFG_AUTO, flags=0, wait_limit_ns=0, batch=1,
+                 stride_a=0, stride_b=0, stride_c=0, stride_d=0):
         it = in_dtype if isinstance(in_dtype, int) else _torch_dtype_code(in_dtype)
         ot = out_dtype if isinstance(out_dtype, int) else _torch_dtype_code(out_dtype)
         self.desc = GemmDesc.make(it, ot, m, n, k, layout_a, layout_b, lda, ldb, ldc, ldd, device,
-                                  config, flags, wait_limit_ns)
+                                  config, flags, wait_limit_ns, batch, stride_a, stride_b, stride_c, stride_d)
         self.plan = Plan(self.desc)
 
     def __call__(self, a, b, c, d, alpha, beta, stream=None):

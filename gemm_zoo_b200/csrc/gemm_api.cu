@@ -146,7 +146,10 @@ gz_status normalise(const gz_gemm_desc* desc, Problem* pr) {
     return GZ_ERR_INVALID_ARG;
   if ((d.flags & GZ_FLAG_NO_SPLIT_K) && (d.flags & GZ_FLAG_SPLIT_K)) return GZ_ERR_INVALID_ARG;
   if (d.flags & ~(GZ_FLAG_EPILOGUE_DIRECT | GZ_FLAG_EPILOGUE_TMA | GZ_FLAG_NO_SPLIT_K | GZ_FLAG_SPLIT_K |
-                  GZ_FLAG_TEST_WITHHOLD_ACC_READY))
+                  GZ_FLAG_BROADCAST_A | GZ_FLAG_BROADCAST_B | GZ_FLAG_TEST_WITHHOLD_ACC_READY))
+    return GZ_ERR_INVALID_ARG;
+  if (d.batch == 0) d.batch = 1;
+  if (d.batch < 0 || d.batch > 65535 || d.stride_a < 0 || d.stride_b < 0 || d.stride_c < 0 || d.stride_d < 0)
     return GZ_ERR_INVALID_ARG;
   if (!pair_supported(d.in_type, d.out_type)) return GZ_ERR_UNSUPPORTED;
   if (d.config != GZ_CFG_AUTO && d.config != GZ_CFG_SIMT && !shape_of(d.config))
@@ -161,7 +164,14 @@ gz_status normalise(const gz_gemm_desc* desc, Problem* pr) {
   // Tile coordinates and TMA coordinates are 32-bit.
   const int64_t lim = (int64_t(1) << 31) - 1024;
   if (d.m > lim || d.n > lim || d.k > lim) return GZ_ERR_TOO_LARGE;
-  if (cdiv(d.m, 128) * cdiv(d.n, 64) > (int64_t(1) << 31) - 1) return GZ_ERR_TOO_LARGE;
+  if (cdiv(d.m, 128) * cdiv(d.n, 64) * d.batch > (int64_t(1) << 31) - 1) return GZ_ERR_TOO_LARGE;
+  // Batch strides: packed by default; a broadcast operand has none.
+  if (d.stride_a == 0) d.stride_a = (d.layout_a == GZ_ROW_MAJOR ? d.m : d.k) * d.lda;
+  if (d.stride_b == 0) d.stride_b = (d.layout_b == GZ_ROW_MAJOR ? d.k : d.n) * d.ldb;
+  if (d.stride_c == 0) d.stride_c = d.m * d.ldc;
+  if (d.stride_d == 0) d.stride_d = d.m * d.ldd;
+  if (d.flags & GZ_FLAG_BROADCAST_A) d.stride_a = 0;
+  if (d.flags & GZ_FLAG_BROADCAST_B) d.stride_b = 0;
   if (d.wait_limit_ns == 0) d.wait_limit_ns = 2000000000ull;
   pr->d = d;
   pr->in_size = dtype_size(d.in_type);
@@ -170,7 +180,11 @@ gz_status normalise(const gz_gemm_desc* desc, Problem* pr) {
   pr->b_mn_major = d.layout_b == GZ_ROW_MAJOR;
   pr->tma_ld_ok = (d.lda * pr->in_size) % 16 == 0 && (d.ldb * pr->in_size) % 16 == 0 &&
                   (d.lda * (int64_t)pr->in_size) < (int64_t(1) << 40) &&
-                  (d.ldb * (int64_t)pr->in_size) < (int64_t(1) << 40);
+                  (d.ldb * (int64_t)pr->in_size) < (int64_t(1) << 40) &&
+                  // the batch dimension of a tensor map is a stride like any other
+                  (d.batch == 1 || ((d.stride_a * pr->in_size) % 16 == 0 && (d.stride_b * pr->in_size) % 16 == 0 &&
+                                    (d.stride_a * (int64_t)pr->in_size) < (int64_t(1) << 40) &&
+                                    (d.stride_b * (int64_t)pr->in_size) < (int64_t(1) << 40)));
   return GZ_OK;
 }
 
@@ -193,7 +207,7 @@ bool shape_fits(const Problem& pr, const CfgShape& s) {
 bool wants_split_k(const Problem& pr, const CfgShape& s, int sm_count) {
   if (!s.swap || (pr.d.flags & GZ_FLAG_NO_SPLIT_K)) return false;
   const int64_t k_blocks = cdiv(pr.d.k, 128 / pr.in_size);
-  const int64_t tiles = cdiv(pr.d.n, 128) * cdiv(pr.d.m, s.bn);
+  const int64_t tiles = cdiv(pr.d.n, 128) * cdiv(pr.d.m, s.bn) * pr.d.batch;
   const int64_t total = tiles * k_blocks;
   if (total < 2) return false;
   if (pr.d.flags & GZ_FLAG_SPLIT_K) return true;
@@ -255,7 +269,7 @@ int choose_config(const Problem& pr, int sm_count) {
   for (const auto& s : kShapes) {
     if (!shape_fits(pr, s)) continue;
     const int64_t wide = s.swap ? pr.d.n : pr.d.m, narrow = s.swap ? pr.d.m : pr.d.n;
-    const int64_t tiles = cdiv(wide, s.tile_wide()) * cdiv(narrow, s.bn);
+    const int64_t tiles = cdiv(wide, s.tile_wide()) * cdiv(narrow, s.bn) * pr.d.batch;
     const int64_t units = sm_count / s.ctas;
     if (units <= 0) continue;
     const double mma = 4.0 * (s.bn / 2.0) * s.mb;
@@ -308,7 +322,7 @@ void fill_info(const Problem& pr, int config, int sm_count, gz_plan_info* info) 
     info->tile_k = 16;
     info->stages = 1;
     info->ctas_per_tile = 1;
-    info->tiles = cdiv(pr.d.m, 64) * cdiv(pr.d.n, 64);
+    info->tiles = cdiv(pr.d.m, 64) * cdiv(pr.d.n, 64) * pr.d.batch;
     info->grid = (int32_t)info->tiles;
     info->smem_bytes = 0;
     return;
@@ -319,7 +333,7 @@ void fill_info(const Problem& pr, int config, int sm_count, gz_plan_info* info) 
   info->tile_k = 128 / pr.in_size;
   info->stages = s->stages;
   info->ctas_per_tile = s->ctas;
-  info->tiles = cdiv(pr.d.m, info->tile_m) * cdiv(pr.d.n, info->tile_n);
+  info->tiles = cdiv(pr.d.m, info->tile_m) * cdiv(pr.d.n, info->tile_n) * pr.d.batch;
   const int64_t units = sm_count / s->ctas;
   info->grid = (int32_t)((info->tiles < units ? info->tiles : units) * s->ctas);
   // Mirrors GemmCfg::SMEM_BYTES: alignment slack, the operand ring, epilogue staging, barriers.
@@ -327,7 +341,9 @@ void fill_info(const Problem& pr, int config, int sm_count, gz_plan_info* info) 
   info->smem_bytes = 1024 + s->stages * (128 * s->mb * 128 + (s->bn / s->ctas) * 128) + staging + 256;
   // Output rows go through shared memory and TMA stores when D's row pitch allows it; the swapped
   // (skinny) tiles hold the transposed tile and always store straight from registers.
-  const bool d_tma_ok = (pr.d.ldd * pr.out_size) % 16 == 0;
+  const bool d_tma_ok = (pr.d.ldd * pr.out_size) % 16 == 0 &&
+                        (pr.d.batch == 1 || ((pr.d.stride_d * pr.out_size) % 16 == 0 &&
+                                             pr.d.stride_d * (int64_t)pr.out_size < (int64_t(1) << 40)));
   info->epilogue_tma = (!s->swap && d_tma_ok && !(pr.d.flags & GZ_FLAG_EPILOGUE_DIRECT)) ? 1 : 0;
   if (wants_split_k(pr, *s, sm_count)) {
     const int64_t k_blocks = cdiv(pr.d.k, info->tile_k);
@@ -454,7 +470,7 @@ KernelEntry entry_for(int in, int out, int config) {
 
 template <typename TIn, typename TOut>
 cudaError_t launch_simt(const gz::SimtParams& sp, cudaStream_t stream) {
-  dim3 grid((unsigned)cdiv(sp.n, 64), (unsigned)cdiv(sp.m, 64), 1);
+  dim3 grid((unsigned)cdiv(sp.n, 64), (unsigned)cdiv(sp.m, 64), (unsigned)(sp.batch > 0 ? sp.batch : 1));
   gz::simt_gemm_kernel<TIn, TOut><<<grid, 256, 0, stream>>>(sp);
   return cudaGetLastError();
 }
@@ -489,20 +505,26 @@ CUtensorMapDataType tmap_type(int dt) {
   }
 }
 
-// 2-D tensor map: dim0 (contiguous) x dim1, row pitch `pitch_bytes`, 128-byte swizzle.
+// Tensor map of a batch of matrices: dim0 (contiguous) x dim1 with row pitch `pitch_bytes`, times
+// `batch` matrices `batch_stride_bytes` apart (a single matrix is a batch of one), 128-byte
+// swizzle, boxes of box0 x box1 x 1.
 bool encode_2d(CUtensorMap* tm, int dt, const void* base, uint64_t dim0, uint64_t dim1,
                uint64_t pitch_bytes, uint32_t box0, uint32_t box1, bool promote,
-               bool swizzle_32b_atom = false) {
+               bool swizzle_32b_atom = false, uint64_t batch = 1, uint64_t batch_stride_bytes = 0) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) {
     g_last_cuda_error = "cuTensorMapEncodeTiled entry point not available";
     return false;
   }
-  cuuint64_t dims[2] = {dim0, dim1};
-  cuuint64_t strides[1] = {pitch_bytes};
-  cuuint32_t box[2] = {box0, box1};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(tm, tmap_type(dt), 2, const_cast<void*>(base), dims, strides, box, estr,
+  if (batch <= 1 || batch_stride_bytes == 0) {  // one matrix (or one shared by the whole batch)
+    batch = 1;
+    batch_stride_bytes = pitch_bytes * dim1;
+  }
+  cuuint64_t dims[3] = {dim0, dim1, batch};
+  cuuint64_t strides[2] = {pitch_bytes, batch_stride_bytes};
+  cuuint32_t box[3] = {box0, box1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, tmap_type(dt), 3, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle_32b_atom ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                   promote ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
@@ -744,14 +766,20 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
     // Rows of tiles that run concurrently should span about as many output rows as columns.
     uint32_t gm = 2048u / tile_m;
     p.grid.group_m = gm < 1 ? 1 : gm;
-    p.grid.num_tiles = p.grid.tiles_m * p.grid.tiles_n;
+    p.grid.num_tiles = p.grid.tiles_m * p.grid.tiles_n;  // per problem of the batch
+    const int64_t all_tiles = (int64_t)p.grid.num_tiles * pr.d.batch;
     {
       int64_t first;
-      const int parts = tail_parts_for(pr, s, p.grid.num_tiles, sm_count / s.ctas, &first);
+      const int parts = tail_parts_for(pr, s, all_tiles, sm_count / s.ctas, &first);
       p.tail_first = (uint32_t)first;
       p.tail_parts = (uint32_t)parts;
-      p.virt_tiles = (uint32_t)(first + (p.grid.num_tiles - first) * parts);
+      p.virt_tiles = (uint32_t)(first + (all_tiles - first) * parts);
     }
+    p.stride_c = pr.d.stride_c;
+    p.stride_d = pr.d.stride_d;
+    // Operand "a" of the kernel is A, or B for the swapped tiles.
+    p.a.broadcast = ((s.swap ? pr.d.stride_b : pr.d.stride_a) == 0) ? 1u : 0u;
+    p.b.broadcast = ((s.swap ? pr.d.stride_a : pr.d.stride_b) == 0) ? 1u : 0u;
     p.m = (uint32_t)wide;
     p.n = (uint32_t)narrow;
     p.k = (uint32_t)pr.d.k;
@@ -777,7 +805,7 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
     p.wait_limit_ns = pr.d.wait_limit_ns;
     if (pl->info.split_k) {
       const size_t ws_bytes = (size_t)pl->info.workspace_bytes;
-      const size_t counter_bytes = (size_t)p.grid.num_tiles * 4;
+      const size_t counter_bytes = (size_t)all_tiles * 4;
       if (!cuda_ok(cudaMalloc(&pl->workspace, ws_bytes), "cudaMalloc(split-K workspace)") ||
           !cuda_ok(cudaMemset(pl->workspace, 0, ws_bytes), "cudaMemset(split-K workspace)")) {
         if (pl->workspace) cudaFree(pl->workspace);
@@ -787,7 +815,7 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
       }
       p.split_k = 1;
       p.max_contrib = (uint32_t)pl->info.reserved;
-      p.total_kb = (unsigned long long)p.grid.num_tiles * p.k_blocks;
+      p.total_kb = (unsigned long long)all_tiles * p.k_blocks;
       p.ws = static_cast<float*>(pl->workspace);
       p.counters = reinterpret_cast<int*>(static_cast<char*>(pl->workspace) + (ws_bytes - counter_bytes));
     }
@@ -865,7 +893,7 @@ gz_status run_impl(gz_plan* pl, const void* a, const void* b, const void* c, voi
     if (bad(ep->bias) || bad(ep->row_scale) || bad(ep->col_scale)) return GZ_ERR_MISALIGNED;
   }
   if (sc) {
-    if (pl->info.config == GZ_CFG_SIMT || pr.out_size != 4 || sc->cols == 0 || sc->cols % 32 != 0 ||
+    if (pl->info.config == GZ_CFG_SIMT || pr.out_size != 4 || pr.d.batch != 1 || sc->cols == 0 || sc->cols % 32 != 0 ||
         sc->parts < 1 || sc->parts > 8 || (int64_t)sc->cols * sc->parts < pr.d.n || sc->ld < sc->cols)
       return GZ_ERR_UNSUPPORTED;
   }
@@ -901,6 +929,11 @@ gz_status run_impl(gz_plan* pl, const void* a, const void* b, const void* c, voi
     sp.b_sn = pr.b_mn_major ? 1 : pr.d.ldb;
     sp.ldc = pr.d.ldc;
     sp.ldd = pr.d.ldd;
+    sp.batch = pr.d.batch;
+    sp.stride_a = pr.d.stride_a;
+    sp.stride_b = pr.d.stride_b;
+    sp.stride_c = pr.d.stride_c;
+    sp.stride_d = pr.d.stride_d;
     sp.alpha_f = af;
     sp.beta_f = bf;
     sp.alpha_i = ai;
@@ -951,25 +984,27 @@ gz_status run_impl(gz_plan* pl, const void* a, const void* b, const void* c, voi
   const uint32_t bk = 128u / pr.in_size;
   // Tensor map of one input matrix: `rows` is its M (or N) extent, `od` the kernel operand it feeds.
   auto encode_input = [&](CUtensorMap* tm, const void* base, bool mn_major, int64_t rows, int64_t ld,
-                          const gz::OperandDesc& od) {
+                          const gz::OperandDesc& od, int64_t batch_stride) {
     if (!mn_major)
       return encode_2d(tm, pr.d.in_type, base, (uint64_t)pr.d.k, (uint64_t)rows, (uint64_t)ld * pr.in_size,
-                       bk, od.box_mn, true);
+                       bk, od.box_mn, true, false, (uint64_t)pr.d.batch, (uint64_t)batch_stride * pr.in_size);
     return encode_2d(tm, pr.d.in_type, base, (uint64_t)rows, (uint64_t)pr.d.k, (uint64_t)ld * pr.in_size,
-                     od.box_mn, bk, true, pr.in_size == 4);
+                     od.box_mn, bk, true, pr.in_size == 4, (uint64_t)pr.d.batch,
+                     (uint64_t)batch_stride * pr.in_size);
   };
   bool ok;
   if (!s.swap) {
-    ok = encode_input(&ta, a, pr.a_mn_major, pr.d.m, pr.d.lda, p.a) &&
-         encode_input(&tb, b, pr.b_mn_major, pr.d.n, pr.d.ldb, p.b);
+    ok = encode_input(&ta, a, pr.a_mn_major, pr.d.m, pr.d.lda, p.a, pr.d.stride_a) &&
+         encode_input(&tb, b, pr.b_mn_major, pr.d.n, pr.d.ldb, p.b, pr.d.stride_b);
   } else {
-    ok = encode_input(&ta, b, pr.b_mn_major, pr.d.n, pr.d.ldb, p.a) &&
-         encode_input(&tb, a, pr.a_mn_major, pr.d.m, pr.d.lda, p.b);
+    ok = encode_input(&ta, b, pr.b_mn_major, pr.d.n, pr.d.ldb, p.a, pr.d.stride_b) &&
+         encode_input(&tb, a, pr.a_mn_major, pr.d.m, pr.d.lda, p.b, pr.d.stride_a);
   }
   if (!ok) return GZ_ERR_CUDA;
   if (p.epilogue_tma) {
     ok = encode_2d(&td, pr.d.out_type, d, (uint64_t)pr.d.n, (uint64_t)pr.d.m,
-                   (uint64_t)pr.d.ldd * pr.out_size, 128u / pr.out_size, 32, false);
+                   (uint64_t)pr.d.ldd * pr.out_size, 128u / pr.out_size, 32, false, false,
+                   (uint64_t)pr.d.batch, (uint64_t)pr.d.stride_d * pr.out_size);
     if (!ok) return GZ_ERR_CUDA;
   } else {
     td = ta;  // unused by the kernel in this mode
@@ -1004,6 +1039,7 @@ GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, con
   if (st != GZ_OK) return st;
   const bool beta_zero = (pr.d.out_type == GZ_DT_S32) ? (bi == 0) : (bf == 0.0f);
   if (!beta_zero && !c) return GZ_ERR_INVALID_ARG;
+  if (pr.d.batch != 1) return GZ_ERR_UNSUPPORTED;  // the host-operand pipeline moves one problem
   DeviceGuard guard(pr.d.device);
   if (!guard.ok()) return GZ_ERR_CUDA;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
@@ -1322,6 +1358,7 @@ extern "C" GZ_API gz_status gz_gemm_skinny_static(const gz_gemm_desc* desc, cons
   const bool beta_zero = (pr.d.out_type == GZ_DT_S32) ? (bi == 0) : (bf == 0.0f);
   if (!beta_zero && !c) return GZ_ERR_INVALID_ARG;
 
+  if (pr.d.batch != 1) return GZ_ERR_UNSUPPORTED;
   StaticScratchDevice* sd = nullptr;
   st = static_scratch_setup(pr.d.device, &sd);
   if (st != GZ_OK) return st;

@@ -134,45 +134,39 @@ __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
 
-// 2-D tile load global -> this CTA's shared memory, completion on this CTA's barrier.
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int32_t c0, int32_t c1,
+// Tile loads and stores use 3-D tensor maps throughout: (contiguous dim, second dim, batch).  A
+// single problem is a batch of one.  Only the innermost coordinate has an alignment rule (its
+// byte offset must be a multiple of 16).
+//
+// Tile load global -> this CTA's shared memory, completion on this CTA's barrier.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int32_t c0, int32_t c1, int32_t c2,
                                             uint32_t bar) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
       :
-      : "r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1)
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 
-// 2-D tile load into this CTA's shared memory whose completion bytes are
-// counted on a barrier that may belong to the peer CTA of a 2-CTA pair
-// (`cluster_bar` is a shared::cluster address).  No multicast: the data lands
-// in the issuing CTA only.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, int32_t c0,
-                                                 int32_t c1, uint32_t cluster_bar) {
+// Tile load into this CTA's shared memory whose completion bytes are counted on a barrier that
+// may belong to the peer CTA of a 2-CTA pair (`cluster_bar` is a shared::cluster address).  No
+// multicast: the data lands in the issuing CTA only.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* tmap, int32_t c0, int32_t c1,
+                                                 int32_t c2, uint32_t cluster_bar) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
       :
-      : "r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(cluster_bar), "r"(c0), "r"(c1)
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 
-// Bring a 2-D tile into L2 only (no shared-memory destination, no barrier).
-__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int32_t c0, int32_t c1) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+// Tile store shared -> global (bulk async-group completion).
+__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src, int32_t c0, int32_t c1, int32_t c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
                :
-               : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1)
-               : "memory");
-}
-
-// 2-D tile store shared -> global (bulk async-group completion).
-__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int32_t c0,
-                                             int32_t c1) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-               :
-               : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(c0), "r"(c1)
+               : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
 }
 __device__ __forceinline__ void bulk_commit_group() {

@@ -27,6 +27,7 @@ struct SimtParams {
   int64_t a_sm, a_sk;  // element strides of A along m and k
   int64_t b_sk, b_sn;  // element strides of B along k and n
   int64_t ldc, ldd;
+  int64_t batch, stride_a, stride_b, stride_c, stride_d;  // problems along blockIdx.z, strides in elements
   float alpha_f, beta_f;
   int32_t alpha_i, beta_i;
   // optional epilogue terms (float outputs): D = act(alpha * rs[i] * cs[j] * acc + beta * C + bias[j])
@@ -92,8 +93,8 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
   __shared__ Acc sa[TK][TM + 1];
   __shared__ Acc sb[TK][TN + 1];
 
-  const TIn* a = static_cast<const TIn*>(p.a);
-  const TIn* b = static_cast<const TIn*>(p.b);
+  const TIn* a = static_cast<const TIn*>(p.a) + static_cast<int64_t>(blockIdx.z) * p.stride_a;
+  const TIn* b = static_cast<const TIn*>(p.b) + static_cast<int64_t>(blockIdx.z) * p.stride_b;
   const int64_t m0 = static_cast<int64_t>(blockIdx.y) * TM;
   const int64_t n0 = static_cast<int64_t>(blockIdx.x) * TN;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -144,8 +145,8 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
     __syncthreads();
   }
 
-  const TOut* c = static_cast<const TOut*>(p.c);
-  TOut* d = static_cast<TOut*>(p.d);
+  const TOut* c = static_cast<const TOut*>(p.c) + static_cast<int64_t>(blockIdx.z) * p.stride_c;
+  TOut* d = static_cast<TOut*>(p.d) + static_cast<int64_t>(blockIdx.z) * p.stride_d;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int64_t gm = m0 + ty * 4 + i;

@@ -66,6 +66,7 @@ struct OperandDesc {
   uint32_t desc_lo;    // shared-memory descriptor bits 16..31 (leading byte offset >> 4) << 16
   uint32_t desc_hi;    // bits 32..63: stride byte offset >> 4, version 1, 128B swizzle
   uint32_t k_step16;   // descriptor start-address advance (bytes >> 4) per MMA K step
+  uint32_t broadcast;  // batched problems: 1 = every problem of the batch reads the same matrix
 };
 
 // Codes written to status[0] when a bounded wait expires.
@@ -91,6 +92,9 @@ struct GemmParams {
   float alpha_f, beta_f;
   int32_t alpha_i, beta_i;
   int64_t ldc, ldd;
+  // Batched problems: tile indices run over batch * grid.num_tiles; problem i of the batch uses
+  // coordinate i of the tensor maps' third dimension and C + i * stride_c, D + i * stride_d.
+  int64_t stride_c, stride_d;  // elements
   const void* c;
   void* d;
   uint32_t* status;  // 4 words in global memory
@@ -142,7 +146,6 @@ struct GemmParams {
 
 enum : uint32_t {
   TUNE_COMMIT_MULTICAST = 1u,  // 2-CTA tiles: one multicast commit instead of two plain commits
-  TUNE_L2_PREFETCH_SHIFT = 8,  // bits 8..15: prefetch operand tiles into L2 this many K blocks ahead
 };
 
 // SWAP_: the roles of the operands are exchanged.  The 128-row side of the MMA (TMEM lanes) walks N
@@ -495,8 +498,9 @@ __device__ __forceinline__ void store_direct(const uint32_t (&v)[32], TOut* drow
 // Address of output element (row, col); col must not be split from its 32-aligned neighbours by a
 // scatter boundary (scatter_cols is a multiple of 32).
 template <typename TOut>
-__device__ __forceinline__ TOut* out_ptr(const GemmParams& p, uint32_t row, uint32_t col) {
-  if (p.scatter_cols == 0u) return static_cast<TOut*>(p.d) + static_cast<int64_t>(row) * p.ldd + col;
+__device__ __forceinline__ TOut* out_ptr(const GemmParams& p, uint32_t row, uint32_t col, uint32_t batch = 0) {
+  if (p.scatter_cols == 0u)
+    return static_cast<TOut*>(p.d) + static_cast<int64_t>(batch) * p.stride_d + static_cast<int64_t>(row) * p.ldd + col;
   const uint32_t owner = col / p.scatter_cols;
   return static_cast<TOut*>(p.scatter_ptrs[owner]) + static_cast<int64_t>(row) * p.ldd +
          (col - owner * p.scatter_cols);
@@ -509,7 +513,7 @@ __device__ __forceinline__ TOut* out_ptr(const GemmParams& p, uint32_t row, uint
 // 32 different rows per instruction would waste the link.
 template <typename TOut>
 __device__ __forceinline__ void store_staged_box(const GemmParams& p, uint32_t stg, uint32_t lane, uint32_t row0,
-                                                 uint32_t box_col) {
+                                                 uint32_t box_col, uint32_t batch) {
   constexpr uint32_t PER16 = 16 / sizeof(TOut);
   const uint32_t j = lane & 7u;
 #pragma unroll
@@ -520,7 +524,7 @@ __device__ __forceinline__ void store_staged_box(const GemmParams& p, uint32_t s
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "r"(stg + r * 128u + ((j ^ (r & 7u)) << 4))
                  : "memory");
-    if (row0 + r < p.m) *reinterpret_cast<uint4*>(out_ptr<TOut>(p, row0 + r, box_col + j * PER16)) = v;
+    if (row0 + r < p.m) *reinterpret_cast<uint4*>(out_ptr<TOut>(p, row0 + r, box_col + j * PER16, batch)) = v;
   }
 }
 
@@ -675,7 +679,6 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const uint32_t my_bytes = is_b ? Cfg::B_BYTES : Cfg::A_BYTES;
     const uint32_t smem_off = is_b ? Cfg::A_BYTES : 0u;
     const uint32_t bk = p.bk;
-    const uint32_t l2_dist = (p.tune >> TUNE_L2_PREFETCH_SHIFT) & 0xFFu;
     uint32_t stage = 0, phase = 0;
     bool ok = true;
     long long prof_wait = 0, prof_issue = 0;
@@ -684,7 +687,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     uint32_t t = 0, kb_lo = 0, kb_hi = 0;
     while (ok && work.next(t, kb_lo, kb_hi)) {
       uint32_t tm, tn;
-      tile_coords(p.grid, t, tm, tn);
+      const uint32_t bidx = t / p.grid.num_tiles;  // problem of the batch
+      tile_coords(p.grid, t - bidx * p.grid.num_tiles, tm, tn);
+      const int32_t bz = od.broadcast ? 0 : static_cast<int32_t>(bidx);
       const int32_t row0 = is_b ? static_cast<int32_t>(tn * BN + work.col_off + rank * (work.cols / CTAS))
                                 : static_cast<int32_t>(tm * (Cfg::BM * CTAS) + rank * Cfg::BM);
       for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
@@ -709,16 +714,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           for (uint32_t i = 0; i < boxes; ++i) {
             const int32_t mn = row0 + static_cast<int32_t>(i * box_mn);
             if constexpr (CTAS == 1)
-              ptx::tma_load_2d(dst + i * box_bytes, tmap, mn_major ? mn : k0, mn_major ? k0 : mn, fb);
+              ptx::tma_load_3d(dst + i * box_bytes, tmap, mn_major ? mn : k0, mn_major ? k0 : mn, bz, fb);
             else
-              ptx::tma_load_2d_pair(dst + i * box_bytes, tmap, mn_major ? mn : k0, mn_major ? k0 : mn, fb);
-          }
-          if (l2_dist != 0u && kb + l2_dist < kb_hi) {
-            const int32_t kp = static_cast<int32_t>((kb + l2_dist) * bk);
-            for (uint32_t i = 0; i < boxes; ++i) {
-              const int32_t mn = row0 + static_cast<int32_t>(i * box_mn);
-              ptx::tma_prefetch_l2_2d(tmap, mn_major ? mn : kp, mn_major ? kp : mn);
-            }
+              ptx::tma_load_3d_pair(dst + i * box_bytes, tmap, mn_major ? mn : k0, mn_major ? k0 : mn, bz, fb);
           }
         }
         __syncwarp();
@@ -949,7 +947,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       uint32_t t = 0, kb_lo = 0, kb_hi = 0;
       while (ok && work.next(t, kb_lo, kb_hi)) {
         uint32_t tm, tn;
-        tile_coords(p.grid, t, tm, tn);
+        const uint32_t bidx = t / p.grid.num_tiles;  // problem of the batch
+        tile_coords(p.grid, t - bidx * p.grid.num_tiles, tm, tn);
+        const TOut* const cmat_b = cmat + static_cast<int64_t>(bidx) * p.stride_c;
         const uint32_t wcols = work.cols / HALVES;  // columns of this piece that belong to this warp
         const uint32_t col_w = tn * BN + work.col_off + half * wcols;
         if constexpr (Cfg::MB == 2 && sizeof(TOut) == 2) {
@@ -1037,13 +1037,13 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   ptx::fence_proxy_async_smem();
                   __syncwarp();
                   if (lane == 0) {
-                    ptx::tma_store_2d(&tm_d, stg, static_cast<int32_t>(col_w + box * BOX_COLS),
-                                      static_cast<int32_t>(row0));
+                    ptx::tma_store_3d(&tm_d, stg, static_cast<int32_t>(col_w + box * BOX_COLS),
+                                      static_cast<int32_t>(row0), static_cast<int32_t>(bidx));
                     ptx::bulk_commit_group();
                   }
                 } else {
                   __syncwarp();
-                  detail::store_staged_box<TOut>(p, stg, lane, row0, col_w + box * BOX_COLS);
+                  detail::store_staged_box<TOut>(p, stg, lane, row0, col_w + box * BOX_COLS, bidx);
                   __syncwarp();
                 }
               }
@@ -1087,7 +1087,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             }
             if (prof) prof_copy += clock64() - c0;
             if (row0 < p.m) {
-              const TOut* crow = cmat + static_cast<int64_t>(row) * p.ldc + col_w;
+              const TOut* crow = cmat_b + static_cast<int64_t>(row) * p.ldc + col_w;
 #pragma unroll
               for (int box = 0; box < WARP_COLS / BOX_COLS; ++box) {
                 if (p.epilogue_tma) {
@@ -1117,13 +1117,13 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   ptx::fence_proxy_async_smem();
                   __syncwarp();
                   if (lane == 0) {
-                    ptx::tma_store_2d(&tm_d, stg, static_cast<int32_t>(col_w + box * BOX_COLS),
-                                      static_cast<int32_t>(row0));
+                    ptx::tma_store_3d(&tm_d, stg, static_cast<int32_t>(col_w + box * BOX_COLS),
+                                      static_cast<int32_t>(row0), static_cast<int32_t>(bidx));
                     ptx::bulk_commit_group();
                   }
                 } else {
                   __syncwarp();
-                  detail::store_staged_box<TOut>(p, stg, lane, row0, col_w + box * BOX_COLS);
+                  detail::store_staged_box<TOut>(p, stg, lane, row0, col_w + box * BOX_COLS, bidx);
                   __syncwarp();
                 }
               }
@@ -1145,7 +1145,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   uint32_t x[32];
                   ptx::tmem_ld_32x32(taddr + box * BOX_COLS + sl * 32u, x);
                   ptx::tmem_wait_ld();
-                  const TOut* crow = cmat + static_cast<int64_t>(row) * p.ldc + col0;
+                  const TOut* crow = cmat_b + static_cast<int64_t>(row) * p.ldc + col0;
                   detail::epilogue_math<TOut, ACC_INT>(x, p, crow, row_ok, ncols, row, col0);
                   if (p.epilogue_tma) {
 #pragma unroll
@@ -1157,7 +1157,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                                    : "memory");
                     }
                   } else if (row_ok) {
-                    TOut* drow = detail::out_ptr<TOut>(p, row, col0);
+                    TOut* drow = detail::out_ptr<TOut>(p, row, col0, bidx);
                     detail::store_direct<TOut>(x, drow, ncols, p.d_vec_ok != 0u);
                   }
                 }
@@ -1165,7 +1165,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                   ptx::fence_proxy_async_smem();
                   __syncwarp();
                   if (lane == 0) {
-                    ptx::tma_store_2d(&tm_d, stg, static_cast<int32_t>(box_col), static_cast<int32_t>(row0));
+                    ptx::tma_store_3d(&tm_d, stg, static_cast<int32_t>(box_col), static_cast<int32_t>(row0),
+                                      static_cast<int32_t>(bidx));
                     ptx::bulk_commit_group();
                   }
                 }
@@ -1209,7 +1210,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     uint32_t t = 0, kb_lo = 0, kb_hi = 0;
     while (ok && work.next(t, kb_lo, kb_hi)) {
       uint32_t tm, tn;
-      tile_coords(p.grid, t, tm, tn);
+      const uint32_t bidx = t / p.grid.num_tiles;  // problem of the batch
+      tile_coords(p.grid, t - bidx * p.grid.num_tiles, tm, tn);
+      const TOut* const cmat_b = cmat + static_cast<int64_t>(bidx) * p.stride_c;
       const long long w0 = prof ? clock64() : 0;
       if (!detail::wait(tmem_full_bar(acc), acc_phase, ab, WAIT_EPILOGUE_TMEM_FULL, t, 0)) {
         ok = false;
@@ -1328,8 +1331,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               // Column i of the slice is output row mrow0 + i; for each, the 32 lanes of the warp
               // write 32 consecutive elements of that row.
               const uint32_t cnt = (p.n - mrow0 < 16u) ? (p.n - mrow0) : 16u;
-              TOut* dp = detail::out_ptr<TOut>(p, mrow0, ncol);
-              const TOut* cp = cmat + static_cast<int64_t>(mrow0) * p.ldc + ncol;
+              TOut* dp = detail::out_ptr<TOut>(p, mrow0, ncol, bidx);
+              const TOut* cp = cmat_b + static_cast<int64_t>(mrow0) * p.ldc + ncol;
               if (has_beta) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i)

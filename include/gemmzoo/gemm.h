@@ -100,6 +100,8 @@ typedef enum gz_config {
 /* flags */
 #define GZ_FLAG_EPILOGUE_DIRECT 0x1u /* registers -> global stores, no TMA store */
 #define GZ_FLAG_EPILOGUE_TMA 0x2u    /* force the shared-memory + TMA-store epilogue */
+#define GZ_FLAG_BROADCAST_A 0x10u    /* batched: every problem reads the same A (stride_a ignored) */
+#define GZ_FLAG_BROADCAST_B 0x20u    /* batched: every problem reads the same B (stride_b ignored) */
 /* Split-K (skinny problems only): the K range of a tile may be shared by several CTAs, which
  * park fp32 partial sums in a workspace owned by the plan; the last CTA to arrive adds them in K
  * order.  Chosen automatically when it balances the SMs better; these flags override the choice.
@@ -123,6 +125,13 @@ typedef struct gz_gemm_desc {
   int64_t m, n, k;
   int64_t lda, ldb, ldc, ldd; /* 0 = packed default for the layout */
   uint64_t wait_limit_ns;     /* 0 = default (2 s); bound on every in-kernel wait */
+  /* Batched GEMM: `batch` independent problems of the same shape in one launch, problem i reading
+   * A + i * stride_a, B + i * stride_b, C + i * stride_c and writing D + i * stride_d (strides in
+   * elements).  batch 0 or 1 = a single problem; a stride of 0 = packed (rows x leading dimension);
+   * stride_a or stride_b may be given as 0 with GZ_FLAG_BROADCAST_A / _B to share one matrix.
+   * No counterpart in the reference. */
+  int64_t batch;
+  int64_t stride_a, stride_b, stride_c, stride_d;
 } gz_gemm_desc;
 
 typedef struct gz_plan gz_plan;
