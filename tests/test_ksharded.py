@@ -146,6 +146,35 @@ def _worker(rank, world, port, out_dir):
         want = _expected(a, b, None, 1, 0, out_t)[:, rank * cols:(rank + 1) * cols]
         ok = ok and torch.equal(d.cpu(), want)
         g.close()
+    # A peer that misses a step: rank 1 stays out of one push (it is between steps, nothing of its
+    # own in flight).  The other ranks' reduce kernels give up after their bounded wait and report
+    # which rank they were waiting for; the contexts stay usable, and once rank 1 has caught up the
+    # same epoch reduces correctly on every rank.
+    m, n, k = 16, 2048, 2048
+    a = _ints((m, k), gz.DT_BF16, 5, device=dev)
+    b = _ints((n, k), gz.DT_BF16, 6, device=dev)
+    k0, k1 = ksharded.k_slice(k, world, rank, 128)
+    g = ksharded.KShardedGemm(m, n, k1 - k0, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR, lda=k, ldb=k,
+                              wait_limit_ns=20_000_000)
+    cols = n // world
+    d = torch.zeros(m, cols, dtype=torch.bfloat16, device=dev)
+    pa, pb = a.data_ptr() + k0 * 2, b.data_ptr() + k0 * 2
+    if rank != 1:
+        g.plan.push(pa, pb)
+        g.plan.reduce(None, d, 1, 0)
+        st, detail = g.plan.status()
+        ok = ok and st == api.GZ_ERR_DEVICE_TIMEOUT and detail[0] == ksharded.WAIT_PEER_FLAG and detail[2] == 1
+    dist.barrier()
+    if rank == 1:
+        g.plan.push(pa, pb)
+        torch.cuda.synchronize()
+    dist.barrier()
+    g.plan.reduce(None, d, 1, 0)
+    torch.cuda.synchronize()
+    ok = ok and g.plan.status()[0] == api.GZ_OK
+    want = _expected(a, b, None, 1, 0, gz.DT_BF16)[:, rank * cols:(rank + 1) * cols]
+    ok = ok and torch.equal(d.cpu(), want)
+    g.close()
     flag = torch.tensor([int(ok)])
     dist.all_reduce(flag)
     if rank == 0:
