@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import time
 from pathlib import Path
 
 import torch
@@ -80,6 +81,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--only", default=None)
+    ap.add_argument("--pause", type=float, default=3.0, help="seconds of idle time between configurations")
     args = ap.parse_args()
     bf16_peak, hbm_peak, src = peaks()
     stream = torch.cuda.Stream()
@@ -136,6 +138,7 @@ def main():
         print(json.dumps(line), flush=True)
         del A, B, C, D, own, lt
         torch.cuda.empty_cache()
+        time.sleep(args.pause)  # let the chip cool: the seconds-scale configurations leave it at its power limit
 
 
 if __name__ == "__main__":

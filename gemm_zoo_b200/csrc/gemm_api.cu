@@ -793,6 +793,8 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
     }
     p.epilogue_tma = pl->info.epilogue_tma;
     p.test_flags = (pr.d.flags & 0x80000000u) ? 1u : 0u;
+    // Skinny problems stream the weight matrix once: spread the tiles' K positions over the HBM channels.
+    if (pr.d.m <= 128) p.tune |= gz::TUNE_K_STAGGER;
     // Developer tuning knobs, read once per plan.
     if (const char* e = std::getenv("GZ_TUNE")) p.tune = (uint32_t)std::strtoul(e, nullptr, 0);
     if (const char* e = std::getenv("GZ_TUNE_GROUP_M")) {
@@ -1411,6 +1413,7 @@ extern "C" GZ_API gz_status gz_gemm_skinny_static(const gz_gemm_desc* desc, cons
   p.epilogue_tma = 0;
   p.ldc = pr.d.ldc;
   p.ldd = pr.d.ldd;
+  p.tune = gz::TUNE_K_STAGGER;  // as gz_gemm_plan_create does for skinny problems (same summation order)
   p.wait_limit_ns = pr.d.wait_limit_ns;
   p.alpha_f = af;
   p.beta_f = bf;

@@ -146,6 +146,13 @@ struct GemmParams {
 
 enum : uint32_t {
   TUNE_COMMIT_MULTICAST = 1u,  // 2-CTA tiles: one multicast commit instead of two plain commits
+  // Tiles start their K range at different K blocks and wrap around.  Set by the plan for skinny
+  // (weight-streaming) problems: all CTAs walking K in step read addresses that differ only by
+  // multiples of the row pitch, which loads the HBM channels unevenly (measured: 24.5 -> 23.4 us at
+  // M = 16, 26.5 -> 24.7 us at M = 128, N = 14336, K = 4096).  The order in which a tile's K blocks
+  // are summed then depends on the tile index, which is why it is not used where results are
+  // expected to be bitwise independent of the tile shape.
+  TUNE_K_STAGGER = 2u,
 };
 
 // SWAP_: the roles of the operands are exchanged.  The 128-row side of the MMA (TMEM lanes) walks N
@@ -692,6 +699,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const int32_t bz = od.broadcast ? 0 : static_cast<int32_t>(bidx);
       const int32_t row0 = is_b ? static_cast<int32_t>(tn * BN + work.col_off + rank * (work.cols / CTAS))
                                 : static_cast<int32_t>(tm * (Cfg::BM * CTAS) + rank * Cfg::BM);
+      const uint32_t nkb = kb_hi - kb_lo;
+      const uint32_t stagger_mul = ((p.tune >> 8) & 0xFFu) ? ((p.tune >> 8) & 0xFFu) : 31u;  // bits 8..15: override
+      const uint32_t rot = (p.tune & TUNE_K_STAGGER) ? (t * stagger_mul) % nkb : 0u;
       for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
         const long long w0 = PROF ? clock64() : 0;
         const bool got = detail::wait(empty_bar(stage), phase ^ 1u, ab, WAIT_PRODUCER_EMPTY, t, kb);
@@ -701,7 +711,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if constexpr (PROF) prof_wait += w1 - w0;
         if (ptx::elect_one()) {
           const uint32_t dst = base + stage * Cfg::STAGE_BYTES + smem_off;
-          const int32_t k0 = static_cast<int32_t>(kb * bk);
+          uint32_t kk = kb + rot;  // K block fetched in this step
+          if (kk >= kb_hi) kk -= nkb;
+          const int32_t k0 = static_cast<int32_t>(kk * bk);
           uint32_t fb;
           if constexpr (CTAS == 1) {
             fb = full_bar(stage);
