@@ -635,6 +635,13 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const detail::Abort ab{abort_flag, p.status, p.wait_limit_ns};
 
   // ------------------------------------------------------------ set-up
+  // The producers need only the mbarriers, which warp 0 initialises itself; the tensor-memory
+  // allocation concerns the MMA and epilogue warps.  So nobody waits for everybody: warp 0 releases
+  // warp 6 through named barrier 2 and the rest through named barrier 3, which the MMA warp joins
+  // after allocating, and the first loads are in flight while tensor memory is still being set up.
+  // With a CTA pair every thread arrives at the cluster barrier as early as it can (warp 0 after
+  // its initialisation, which is what the peer must not run ahead of) and waits on it only when
+  // it is about to touch the peer.
   if (warp == 0) {
     for (uint32_t s = lane; s < STAGES; s += 32u) {
       ptx::mbar_init(full_bar(s), 2);  // one arrive.expect_tx per producer warp
@@ -650,21 +657,27 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       *split_flag = 0u;
     }
     ptx::fence_mbar_init_cluster();
+    __syncwarp();
+    ptx::named_barrier_arrive(2, 64);
+    ptx::named_barrier_arrive(3, Cfg::THREADS - 32);
+    if constexpr (CTAS == 2) ptx::cluster_arrive_release();
     if (lane == 3u) ptx::prefetch_tensormap(&tm_a);
     if (lane == 4u && p.epilogue_tma) ptx::prefetch_tensormap(&tm_d);
+  } else if (warp == 6) {
+    if constexpr (CTAS == 2) ptx::cluster_arrive_release();
+    if (lane == 0) ptx::prefetch_tensormap(&tm_b);
+    ptx::named_barrier_sync(2, 64);
+  } else {
+    if constexpr (CTAS == 2) ptx::cluster_arrive_release();
+    if (warp == 1) {
+      ptx::tmem_alloc<CTAS>(ptx::smem_u32(tmem_slot), Cfg::TMEM_COLS);
+      ptx::tmem_relinquish<CTAS>();
+    }
+    ptx::tc_fence_before_sync();
+    ptx::named_barrier_sync(3, Cfg::THREADS - 32);
+    ptx::tc_fence_after_sync();
   }
-  if (warp == 6 && lane == 0) ptx::prefetch_tensormap(&tm_b);
-  if (warp == 1) {
-    ptx::tmem_alloc<CTAS>(ptx::smem_u32(tmem_slot), Cfg::TMEM_COLS);
-    ptx::tmem_relinquish<CTAS>();
-  }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  if constexpr (CTAS == 2) {
-    ptx::cluster_arrive_release();
-    ptx::cluster_wait_acquire();
-  }
-  ptx::tc_fence_after_sync();
+  if constexpr (CTAS == 2) ptx::cluster_wait_acquire();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   if constexpr (PROF) {
     if (p.prof && threadIdx.x == 32) p.prof[16 * blockIdx.x + 14] = clock64() - kernel_t0;
