@@ -643,6 +643,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   // its initialisation, which is what the peer must not run ahead of) and waits on it only when
   // it is about to touch the peer.
   if (warp == 0) {
+    // The descriptor fetches are the first thing on the path to the first operand bytes.
+    if (lane == 31u) ptx::prefetch_tensormap(&tm_a);
+    if (lane == 30u && p.epilogue_tma) ptx::prefetch_tensormap(&tm_d);
     for (uint32_t s = lane; s < STAGES; s += 32u) {
       ptx::mbar_init(full_bar(s), 2);  // one arrive.expect_tx per producer warp
       ptx::mbar_init(empty_bar(s), 1);
@@ -661,11 +664,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     ptx::named_barrier_arrive(2, 64);
     ptx::named_barrier_arrive(3, Cfg::THREADS - 32);
     if constexpr (CTAS == 2) ptx::cluster_arrive_release();
-    if (lane == 3u) ptx::prefetch_tensormap(&tm_a);
-    if (lane == 4u && p.epilogue_tma) ptx::prefetch_tensormap(&tm_d);
   } else if (warp == 6) {
-    if constexpr (CTAS == 2) ptx::cluster_arrive_release();
     if (lane == 0) ptx::prefetch_tensormap(&tm_b);
+    if constexpr (CTAS == 2) ptx::cluster_arrive_release();
     ptx::named_barrier_sync(2, 64);
   } else {
     if constexpr (CTAS == 2) ptx::cluster_arrive_release();
