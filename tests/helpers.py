@@ -2,7 +2,7 @@
 layout, run the CUDA path through the C ABI, run the CPU oracle on the same
 values, and compare.
 
-Error bars (also quoted in DESIGN.md):
+Error bars:
   s8 -> s32                      bit-exact
   exact-integer inputs, any type bit-exact after one rounding to the output type
   fp16/bf16 inputs, random       |D - R| <= 2^-8 * |R| + 2^-20 * S   (bf16 out)
