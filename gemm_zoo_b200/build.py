@@ -4,13 +4,14 @@
     python -m gemm_zoo_b200.build lib        # libgemmzoo.so only
 
 Targets
-  lib        gemm_zoo_b200/libgemmzoo.so        the C ABI + sm_100a kernels
+  lib        gemm_zoo_b200/libgemmzoo.so        the C ABI + sm_100a kernels (one object per
+                                                 translation unit, compiled in parallel)
   cublaslt   gemm_zoo_b200/libgz_cublaslt.so    cuBLASLt comparator (bench/tests only)
-  oracle     oracle/liboracle.so                CPU restatement of the reference GEMM (checker)
-  ref        oracle/_ref/libref_kernels.so      the reference project's own kernels, compiled
-                                                 from its sources where they lie (only when
-                                                 those sources are present on this machine)
   bench      gemm_zoo_b200/nvidia/bench/build/* bench mains built against the C++ functor
+
+The CPU oracle and the reference-kernel wrapper are test infrastructure and build from
+oracle/build.py, not from here.  The same library can be built with the CMakeLists.txt at the
+repository root.
 """
 from __future__ import annotations
 
@@ -18,16 +19,16 @@ import os
 import shutil
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
 CSRC = PKG / "csrc"
 INCLUDE = ROOT / "include"
-ORACLE = ROOT / "oracle"
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-NVCC_COMMON = ["-lineinfo", "-O3", "-std=c++17"]
+NVCC_COMMON = ["-lineinfo", "-O3", "-std=c++17", "-Xfatbin", "-compress-all"]
 
 
 def nvcc_path() -> str:
@@ -53,18 +54,36 @@ def _run(cmd, verbose):
     return r.stdout + r.stderr
 
 
-def build_lib(force=False, verbose=False, ptxas_info=False) -> Path:
+def lib_sources():
+    """Translation units of libgemmzoo.so: the host layer and one kernel table per pair of types."""
+    return [CSRC / "gemm_api.cu"] + sorted((CSRC / "inst").glob("*.cu"))
+
+
+def build_lib(force=False, verbose=False, ptxas_info=False, jobs=None) -> Path:
     out = PKG / "libgemmzoo.so"
-    srcs = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(
-        (INCLUDE / "gemmzoo").glob("*.h"))
-    if force or _newer(out, srcs):
-        cmd = [nvcc_path(), *ARCH, *NVCC_COMMON, "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared",
-               f"-I{INCLUDE}", f"-I{CSRC}", "-o", out, CSRC / "gemm_api.cu"]
+    headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list((INCLUDE / "gemmzoo").glob("*.h"))
+    objdir = CSRC / "build"
+    objdir.mkdir(exist_ok=True)
+    todo, objs = [], []
+    for src in lib_sources():
+        obj = objdir / (src.stem + ".o")
+        objs.append(obj)
+        if force or _newer(obj, [src] + headers):
+            cmd = [nvcc_path(), *ARCH, *NVCC_COMMON, "-Xcompiler", "-fPIC,-fvisibility=hidden", "-c",
+                   f"-I{INCLUDE}", f"-I{CSRC}", "-o", obj, src]
+            if ptxas_info:
+                cmd += ["-Xptxas", "-v"]
+            todo.append(cmd)
+    if todo:
+        with ThreadPoolExecutor(max_workers=jobs or min(len(todo), os.cpu_count() or 1)) as pool:
+            logs = list(pool.map(lambda c: _run(c, verbose), todo))
         if ptxas_info:
-            cmd += ["-Xptxas", "-v"]
-        log = _run(cmd, verbose)
-        if ptxas_info:
-            print(log)
+            print("\n".join(logs))
+    if todo or force or _newer(out, objs):
+        # link beside the target and rename: a reader never sees a half-written library
+        tmp = out.with_suffix(".so.tmp")
+        _run([nvcc_path(), *ARCH, "-shared", "-Xcompiler", "-fPIC", "-o", tmp, *objs], verbose)
+        os.replace(tmp, out)
     return out
 
 
@@ -74,36 +93,6 @@ def build_cublaslt(force=False, verbose=False) -> Path:
     if force or _newer(out, [src, PKG / "nvidia" / "kernel_functors" / "cublaslt_gemm.cuh"]):
         cmd = [nvcc_path(), *ARCH, *NVCC_COMMON, "-Xcompiler", "-fPIC", "-shared", f"-I{INCLUDE}",
                f"-I{PKG / 'nvidia'}", "-o", out, src, "-lcublasLt"]
-        _run(cmd, verbose)
-    return out
-
-
-def build_oracle(force=False, verbose=False) -> Path:
-    out = ORACLE / "liboracle.so"
-    src = ORACLE / "ref_gemm.cpp"
-    if force or _newer(out, [src]):
-        cmd = [os.environ.get("GXX", "/usr/bin/g++"), "-O3", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-shared", "-std=c++17",
-               "-ffp-contract=off", "-o", out, src]
-        _run(cmd, verbose)
-    return out
-
-
-def reference_root() -> Path | None:
-    p = Path(os.environ.get("GEMMZOO_REFERENCE", "/root/reference"))
-    return p if (p / "nvidia" / "kernels" / "generic_gemm.cuh").exists() else None
-
-
-def build_ref(force=False, verbose=False) -> Path | None:
-    """Compile the reference project's kernels from its own sources (never copied)."""
-    ref = reference_root()
-    out = ORACLE / "_ref" / "libref_kernels.so"
-    if ref is None:
-        return out if out.exists() else None
-    src = ORACLE / "ref_kernels_wrap.cu"
-    if force or _newer(out, [src]):
-        out.parent.mkdir(parents=True, exist_ok=True)
-        cmd = [nvcc_path(), *ARCH, *NVCC_COMMON, "-Xcompiler", "-fPIC", "-shared",
-               f"-I{ref / 'nvidia'}", "-o", out, src]
         _run(cmd, verbose)
     return out
 
@@ -128,10 +117,6 @@ def build_all(force=False, verbose=False):
     res = {"lib": build_lib(force, verbose)}
     if (PKG / "cmp" / "cublaslt_cmp.cu").exists():
         res["cublaslt"] = build_cublaslt(force, verbose)
-    if (ORACLE / "ref_gemm.cpp").exists():
-        res["oracle"] = build_oracle(force, verbose)
-    if (ORACLE / "ref_kernels_wrap.cu").exists():
-        res["ref"] = build_ref(force, verbose)
     if list((PKG / "nvidia" / "bench").glob("*.cu")):
         res["bench"] = build_bench(force, verbose)
     return res
@@ -148,10 +133,6 @@ if __name__ == "__main__":
             print(build_lib(force, True, ptxas_info=True))
         elif w == "cublaslt":
             print(build_cublaslt(force, True))
-        elif w == "oracle":
-            print(build_oracle(force, True))
-        elif w == "ref":
-            print(build_ref(force, True))
         elif w == "bench":
             print(build_bench(force, True))
         else:

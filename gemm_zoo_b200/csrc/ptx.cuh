@@ -247,17 +247,6 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
   }
 }
 
-// 2-CTA pair only: one commit that arrives on the barrier at the same offset in
-// both CTAs of the pair (CTA mask 0b11).
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
-  const uint16_t mask = 3;
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
-          bar),
-      "h"(mask)
-      : "memory");
-}
-
 enum class Kind : int { F16 = 0, TF32 = 1, I8 = 2, F8 = 3 };
 
 // D[tmem] (+)= A[smem desc] * B[smem desc]; issued by ONE thread.

@@ -34,8 +34,9 @@ def _built():
     """Build the native pieces in-tree if they are missing (staleness is handled by
     __graft_entry__.build(), which compares time stamps)."""
     from gemm_zoo_b200 import build as b
+    from oracle import build as ob
     if not (b.PKG / "libgemmzoo.so").exists():
         b.build_lib()
-    if not (b.ORACLE / "liboracle.so").exists():
-        b.build_oracle()
+    if not (ob.ORACLE / "liboracle.so").exists():
+        ob.build_oracle()
     yield
