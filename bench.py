@@ -4,27 +4,39 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-One JSON line on stdout (rank 0).  A "step" is one GEMM over one set of
-synthetic operands.
+One JSON line on stdout (rank 0).  A "step" is one GEMM over one set of synthetic operands.
 
-Workload (N = 1): bf16 x bf16 -> fp32 accumulate -> bf16, M = N = K = 8192, A
-row-major, B column-major, alpha = 1, beta = 0, seeded N(0,1) / N(0,1)*K^-1/2
-operands generated on the device by gz_fill.  Three operand sets (384 MiB each,
-larger than the 126 MB L2) are rotated so that no step finds its inputs in L2.
-With N > 1 GPUs every rank runs the same slab on its own GPU: the global problem
-is M = K = 8192, N = 8192 * N_gpus with B sharded by column blocks and A
-replicated, no collective on the data path (weak scaling).
+Headline workload: bf16 x bf16 -> fp32 accumulate -> bf16, M = N = K = 8192, A row-major, B
+column-major, alpha = 1, beta = 0, seeded N(0,1) / N(0,1) * K^-1/2 operands generated on the device
+by gz_fill.  Three operand sets (384 MiB each, larger than the 126 MB L2) are rotated so that no
+step finds its inputs in L2.  With N > 1 GPUs every rank runs the same slab on its own GPU (global
+problem M = K = 8192, N = 8192 * N_gpus, B sharded by column blocks, A replicated, no collective on
+the data path: weak scaling).  The timed region of K steps is repeated `--repeats` times, each
+bracketed by a barrier and a device synchronisation; `value` is the median repeat (max over ranks),
+and the spread is reported beside the SM clock sampled during each repeat.
 
 Keys beyond the base contract:
-  roofline      tensor-bound: achieved = 2MNK / mean kernel time (CUDA events on the
-                launching stream), peak = measured cuBLAS bf16 burst (MEASURED_PEAKS.json)
-  cpu_baseline  the CPU restatement of the reference's naive GEMM (oracle/), OpenMP over
-                all host cores, timed on a bounded row sample of the same workload
-  e2e           same metric through gz_gemm_run_host with pinned HOST operands: H2D of A
-                and B and D2H of D inside the timed region
-  cublaslt      cuBLASLt on the same operands in the same process, interleaved
-  sustained     (--sustain S) seconds-long loops of own kernel and cuBLASLt: TFLOP/s, SM clock, watts
-  other_dtypes  fp16 / tf32 / s8 / fp8 at 8192^3 and the bf16 4096^3 beta=0.5 config (own | cuBLASLt)
+  roofline            tensor-bound: achieved = 2MNK / mean kernel time of the median repeat (CUDA
+                      events on the launching stream), peak = the measured cuBLAS bf16 burst;
+                      traffic = DRAM bytes per launch from the committed ncu summary of exactly this
+                      kernel configuration and workload (null when none matches)
+  roofline_sustained  the same kernel in a seconds-long loop against the measured sustained peak
+  sustained           seconds-long loops of own kernel and cuBLASLt: TFLOP/s, SM clock, watts
+  partitioned         the column-partitioned configuration: ONE bf16 16384^3 problem, rank g
+                      computing column block g of N over the N GPUs (strong scaling), each rank's
+                      block checked against the CPU oracle on seeded rows and by a row-sum checksum
+  e2e                 the headline metric through the host-operand entry points with pinned HOST
+                      operands, host<->device copies inside the timed region (1 GPU:
+                      gz_gemm_run_host; N GPUs: each rank uploads 1/N of the replicated A and the
+                      slices are all-gathered over NVLink)
+  configs             every benchmark configuration of the specification on one GPU, own kernel
+                      beside cuBLASLt (device time per launch from CUDA-graph replays), each with its
+                      roofline
+  cublaslt            cuBLASLt on the headline operands in the same process, interleaved
+  cpu_baseline        the CPU restatement of the reference's naive GEMM (oracle/), OpenMP over all
+                      host cores, timed on a bounded row sample of the headline workload
+  ksharded            (N > 1) K-sharded GEMM with the reduce-scatter fused into the epilogue, beside
+                      the GEMM + NCCL reduce-scatter route
 """
 from __future__ import annotations
 
@@ -40,14 +52,16 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 M = N = K = 8192
+PART = 16384  # the column-partitioned configuration is PART^3
 NOMINAL_BF16_TFLOPS = 2250.0
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the bench kernel
-# (profiles/sm100_gemm_bf16_8192_512x256.md); algorithmic bytes are 3 * 128 MiB.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.037e9
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+L2_BYTES = 126 << 20
+METRIC = "bf16 GEMM TFLOP/s at M=N=K=8192"
 
 
 def load_peaks():
+    """Measured peaks of this pool (a JSON file beside this script, written by whoever measured
+    them), else the stated fallback figures."""
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         try:
@@ -58,12 +72,29 @@ def load_peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
+def committed_traffic(kernel_config, m, n, k, in_name, out_name):
+    """DRAM bytes per launch for (kernel configuration, problem) from the table of ncu captures under
+    profiles/; None when the table has no row for exactly this kernel configuration and problem."""
+    table = ROOT / "profiles" / "dram_traffic_per_launch.txt"
+    if not table.exists():
+        return None
+    for line in table.read_text().splitlines():
+        f = line.split()
+        if len(f) >= 7 and not line.startswith("#"):
+            try:
+                if (int(f[0]), int(f[1]), int(f[2]), int(f[3]), f[4], f[5]) == (kernel_config, m, n, k, in_name, out_name):
+                    return float(f[6])
+            except ValueError:
+                continue
+    return None
+
+
 class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    """Samples SM clock, power and throttle reasons through NVML while timed regions run."""
 
     def __init__(self, index):
         self.index = index
-        self.samples = []
+        self.samples = []  # (time, sm_mhz, watts)
         self.reasons = set()
         self.max_mhz = None
         self._stop = threading.Event()
@@ -90,7 +121,12 @@ class ClockSampler:
         }
         while not self._stop.is_set():
             try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    watts = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                except Exception:
+                    watts = None
+                self.samples.append((time.perf_counter(), mhz, watts))
                 r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
                 for bit, name in names.items():
                     if r & bit:
@@ -104,13 +140,20 @@ class ClockSampler:
             self._thread = threading.Thread(target=self._loop, daemon=True)
             self._thread.start()
 
+    def median_mhz(self, t0=None, t1=None):
+        s = sorted(m for (t, m, _) in self.samples if (t0 is None or t >= t0) and (t1 is None or t <= t1))
+        return s[len(s) // 2] if s else None
+
+    def median_watts(self, t0=None, t1=None):
+        s = sorted(w for (t, _, w) in self.samples if w is not None and (t0 is None or t >= t0) and (t1 is None or t <= t1))
+        return s[len(s) // 2] if s else None
+
     def stop(self):
         if self._thread:
             self._stop.set()
             self._thread.join()
-        s = sorted(self.samples)
-        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(s)}
+        return {"sm_mhz": self.median_mhz(), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
 
 
 def physical_gpu_index(local_rank):
@@ -123,11 +166,24 @@ def physical_gpu_index(local_rank):
     return local_rank
 
 
+def workload_name(gpus):
+    base = ("bf16xbf16->fp32acc->bf16 GEMM M=N=K=8192, A row-major, B column-major, alpha=1 beta=0, "
+            "3 rotating operand sets of 384 MiB (inputs larger than L2)")
+    if gpus > 1:
+        base += f"; x{gpus} GPUs: N sharded by column blocks (global N={N * gpus}), A replicated, no collective"
+    return base
+
+
+def config_dict(gpus):
+    return {"workload": workload_name(gpus), "l2": "inputs larger than L2, 3 operand sets rotated"}
+
+
+# ------------------------------------------------------------------ CPU baseline / reference arm
 _CPU_DATA = {}
 
 
 def cpu_reference_tflops(rows, threads=None):
-    """Time the CPU oracle on `rows` rows of the bench workload; returns (TFLOP/s, seconds, cores)."""
+    """Time the CPU oracle on `rows` rows of the headline workload; returns (TFLOP/s, seconds, cores)."""
     import numpy as np
     from oracle import cpu_oracle as orc
     # torch.distributed.run exports OMP_NUM_THREADS=1 to its ranks; the baseline is
@@ -164,11 +220,11 @@ def run_reference(args, rank):
     value = sum(ts) / len(ts)
     sample = f"{rows} of {M} rows of A per step (all {N} columns, K={K}); fp64 accumulation; scaled by 2*rows*N*K"
     line = {
-        "impl": "reference", "metric": "bf16 GEMM TFLOP/s at M=N=K=8192", "value": value, "unit": "TFLOP/s",
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": workload_name(args.gpus), "sample": sample},
+        "config": config_dict(args.gpus),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -176,165 +232,162 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def workload_name(gpus):
-    base = ("bf16xbf16->fp32acc->bf16 GEMM M=N=K=8192, A row-major, B column-major, alpha=1 beta=0, "
-            "3 rotating operand sets of 384 MiB (inputs larger than L2)")
-    if gpus > 1:
-        base += f"; x{gpus} GPUs: N sharded by column blocks (global N={N * gpus}), A replicated, no collective"
-    return base
+# ------------------------------------------------------------------ helpers
+class Ctx:
+    """What every leg needs: torch, the binding, the device, the launching stream, the ranks."""
+
+    def __init__(self, torch, dist, gz, dev, stream, rank, world, local_rank):
+        self.torch, self.dist, self.gz, self.dev, self.stream = torch, dist, gz, dev, stream
+        self.rank, self.world, self.local_rank = rank, world, local_rank
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize(self.dev)
+
+    def max_over_ranks(self, values):
+        t = self.torch.tensor(list(values), dtype=self.torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
+
+    def all_ok(self, flag):
+        t = self.torch.tensor([0 if flag else 1], dtype=self.torch.int32, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return int(t.item()) == 0
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="own", choices=["own", "reference"])
-    ap.add_argument("--no-extras", action="store_true", help="skip cuBLASLt / other dtypes / CPU baseline")
-    ap.add_argument("--sustain", type=float, default=0.0,
-                    help="also run own kernel and cuBLASLt back to back for this many seconds each and "
-                         "report throughput, SM clock and board power under the power cap")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "own" else args.warmup
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-
-    if args.impl == "reference":
-        run_reference(args, rank)
-        return
-
-    import torch
-    import torch.distributed as dist
-    import gemm_zoo_b200 as gz
-
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists for the product path)")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    gz.lib()  # fail loudly if the extension is missing
-    SETS = 3
-    bf16 = torch.bfloat16
-    A = [torch.empty(M, K, dtype=bf16, device=dev) for _ in range(SETS)]
-    B = [torch.empty(N, K, dtype=bf16, device=dev) for _ in range(SETS)]  # column-major K x N
-    D = torch.empty(M, N, dtype=bf16, device=dev)
-    for i in range(SETS):
-        # A is replicated across ranks (same seed); each rank owns its own column block of B.
-        gz.fill(A[i], 1000 + i, 1, 1, 1.0)
-        gz.fill(B[i], 2000 + i, 2 + rank, 1, K ** -0.5)
-    gemm = gz.Sm100Gemm(M, N, K, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR, device=local_rank)
-    info = gemm.info()
-    stream = torch.cuda.current_stream(dev)
-    flops = 2.0 * M * N * K
-
-    def step(i):
-        gemm(A[i % SETS], B[i % SETS], None, D, 1.0, 0.0, stream)
-
-    for i in range(args.warmup):
-        step(i)
-    barrier()
-    sampler = ClockSampler(physical_gpu_index(local_rank))
-    sampler.start()
+def timed_region(cx, fn, steps):
+    """K steps between two events on the launching stream, a barrier and a synchronise either side.
+    Returns (ms on this rank, host time at start, host time at end)."""
+    torch = cx.torch
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record(stream)
-    for i in range(args.steps):
+    cx.barrier()
+    t0 = time.perf_counter()
+    e0.record(cx.stream)
+    for i in range(steps):
+        fn(i)
+    e1.record(cx.stream)
+    cx.barrier()
+    t1 = time.perf_counter()
+    return e0.elapsed_time(e1), t0, t1
+
+
+# ------------------------------------------------------------------ the column-partitioned configuration
+def partitioned_leg(cx, steps, warmup):
+    """ONE bf16 PART^3 problem (A row-major, B column-major, N(0,1)/128, seed 5): rank g computes
+    the column block gz_partition_columns gives it.  Aggregate = 2 * PART^3 / max-over-ranks time.
+    Parity per rank: 16 seeded rows of its block against the CPU oracle (fp64 accumulation) and a
+    row-sum checksum over the whole block."""
+    import numpy as np
+    torch, gz = cx.torch, cx.gz
+    from gemm_zoo_b200.partition import PartitionedGemm
+    from oracle import cpu_oracle as orc
+    n = PART
+    bf16 = torch.bfloat16
+    a = torch.empty(n, n, dtype=bf16, device=cx.dev)
+    b_full = torch.empty(n, n, dtype=bf16, device=cx.dev)  # column-major K x N: row j is column j of B
+    gz.fill(a, 5, 1, 1, 1.0 / 128)
+    gz.fill(b_full, 5, 2, 1, 1.0 / 128)  # every rank generates the same global B and keeps its block
+    pg = PartitionedGemm(n, n, n, gz.DT_BF16, gz.DT_BF16, cx.rank, cx.world, cx.local_rank)
+    lo, hi = pg.col_begin, pg.col_end
+    b = b_full[lo:hi]
+    d = torch.empty(n, hi - lo, dtype=bf16, device=cx.dev)
+    info = pg.info()
+
+    def step(_):
+        pg(a, b, None, d, 1.0, 0.0, cx.stream)
+
+    for i in range(warmup):
         step(i)
-    e1.record(stream)
-    barrier()
-    clocks = sampler.stop()
-    ms_total = e0.elapsed_time(e1)
-    status, detail = gemm.plan.device_status(stream)
-    if status != 0:
-        raise SystemExit(f"device status {status} {detail}")
-    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total_max = float(t.item())
-    ms_per_step = ms_total_max / args.steps
-    value = world * flops / (ms_per_step * 1e-3) / 1e12
-
-    # ---- end to end through the C ABI with host operands (pinned), copies inside the timed region
-    ha = torch.empty(M, K, dtype=bf16).pin_memory()
-    hb = torch.empty(N, K, dtype=bf16).pin_memory()
-    hd = torch.empty(M, N, dtype=bf16).pin_memory()
-    ha.copy_(A[0])
-    hb.copy_(B[0])
-    e2e_steps = max(3, min(args.steps, 10))
-    for _ in range(2):
-        gemm.plan.run_host(ha, hb, None, hd, 1.0, 0.0, stream)
-    barrier()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record(stream)
-    for _ in range(e2e_steps):
-        gemm.plan.run_host(ha, hb, None, hd, 1.0, 0.0, stream)
-    e3.record(stream)
-    barrier()
-    t2 = torch.tensor([e2.elapsed_time(e3)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t2.item()) / e2e_steps
-    e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
-    checksum = float(hd[:4, :4].float().abs().sum())  # the D2H result is read on the host
-
-    peaks, peak_kind = load_peaks()
-    peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
-    achieved = flops / (ms_total / args.steps * 1e-3) / 1e12  # this rank's kernel
-    line = {
-        "metric": "bf16 GEMM TFLOP/s at M=N=K=8192", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": workload_name(world), "l2": "inputs larger than L2, 3 operand sets rotated",
-                   "kernel": {"config": info.config, "tile": [info.tile_m, info.tile_n, info.tile_k],
-                              "stages": info.stages, "ctas_per_tile": info.ctas_per_tile, "grid": info.grid,
-                              "epilogue_tma": info.epilogue_tma}},
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
-                     "frac": achieved / peak_tf, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                     "peak_source": f"{peak_kind} cuBLAS bf16 burst", "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS,
-                     "algorithmic_flops_per_launch": flops,
-                     "algorithmic_bytes_per_launch": 3 * M * N * 2},
-        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
-                "d2h_bytes_per_step": M * N * 2, "ms_per_step": e2e_ms, "steps": e2e_steps,
-                "result_checksum": checksum},
-        "gpu_launches": args.steps,
-        "clocks": clocks,
+    ms, _, _ = timed_region(cx, step, steps)
+    ms_max = cx.max_over_ranks([ms])[0]
+    st, detail = pg.gemm.plan.device_status(cx.stream)
+    # ---- parity of this rank's block
+    rows = np.sort(np.random.default_rng(5 + cx.rank).choice(n, size=16, replace=False))
+    ri = torch.from_numpy(rows).to(cx.dev)
+    ah = orc.bits_of(a[ri])
+    bh = orc.bits_of(b)
+    orc.lib().oracle_set_threads(max(1, len(os.sched_getaffinity(0)) // max(1, cx.world)))
+    ref = orc.gemm_f64(orc.DT_BF16, orc.DT_BF16, ah, bh, None, 16, hi - lo, n, b_col_major=True)
+    scale = orc.abs_gemm(orc.DT_BF16, ah, bh, 16, hi - lo, n, b_col_major=True)
+    got = d[ri].double().cpu().numpy()
+    err = np.abs(got - ref)
+    rows_ok = bool((err <= 2.0 ** -8 * np.abs(ref) + 2.0 ** -20 * scale + 1e-7).all()) and bool(np.isfinite(got).all())
+    # sum_j D[i, j] == A[i, :] . (sum_j B[:, j]) over this rank's columns, every row
+    bsum = b.double().sum(dim=0)
+    want = torch.empty(n, dtype=torch.float64, device=cx.dev)
+    wscale = torch.empty_like(want)
+    babs = b.double().abs().sum(dim=0)
+    for r0 in range(0, n, 2048):
+        blk = a[r0:r0 + 2048].double()
+        want[r0:r0 + 2048] = blk @ bsum
+        wscale[r0:r0 + 2048] = blk.abs() @ babs
+    gsum = d.double().sum(dim=1)
+    dabs = d.double().abs().sum(dim=1)
+    sum_ok = bool(((gsum - want).abs() <= 2.0 ** -9 * dabs + 2.0 ** -18 * wscale).all())
+    ok = cx.all_ok(rows_ok and sum_ok and st == 0)
+    flops = 2.0 * n * n * n
+    out = {
+        "workload": f"bf16 {n}^3, A row-major replicated, B column-major sharded by N over {cx.world} GPU(s) "
+                    "(gz_partition_columns), D shards local, no collective; strong scaling",
+        "value": flops / (ms_max / steps * 1e-3) / 1e12, "unit": "TFLOP/s", "scaling": "strong",
+        "ms_per_step": ms_max / steps, "steps": steps, "warmup": warmup,
+        "rank0_columns": [lo, hi], "rank0_kernel": {"config": info.config, "tile": [info.tile_m, info.tile_n, info.tile_k],
+                                                    "grid": info.grid, "tiles": info.tiles},
+        "parity": "ok" if ok else "FAILED",
+        "parity_detail": {"oracle_rows_per_rank": 16, "rank0_max_err_over_scale": float((err / np.maximum(scale, 1e-30)).max()),
+                          "row_sum_checksum": "all rows of every rank's block", "device_status": st},
+        "gpu_launches": steps,
     }
-
-    if rank == 0 and world == 1 and args.sustain > 0:
-        line["sustained"] = sustained_compare(gz, torch, dev, stream, A, B, D, gemm, flops, args.sustain,
-                                              physical_gpu_index(local_rank))
-    if rank == 0 and world == 1 and not args.no_extras:
-        try:
-            line["cublaslt"] = compare_cublaslt(gz, torch, dev, stream, A, B, D, gemm, flops)
-        except Exception as e:  # the comparator is optional equipment
-            line["cublaslt"] = {"error": repr(e)}
-        try:
-            line["other_dtypes"] = other_dtypes(gz, torch, dev, stream)
-        except Exception as e:
-            line["other_dtypes"] = {"error": repr(e)}
-        rows = 2048 if (os.cpu_count() or 1) >= 32 else 512
-        tf, dt, cores = cpu_reference_tflops(rows)
-        line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                                "sample": f"{rows} of {M} rows of A (all columns, full K), {dt:.1f} s, fp64 accumulation"}
-    elif rank == 0:
-        line["cpu_baseline"] = None
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    if rank == 0:
-        print(json.dumps(line), flush=True)
+    del a, b_full, b, d, want, wscale
+    torch.cuda.empty_cache()
+    return out
 
 
+# ------------------------------------------------------------------ end to end with host operands
+def e2e_leg(cx, gemm, A0, B0, steps):
+    """The headline GEMM with pinned HOST operands, copies inside the timed region.  One GPU:
+    gz_gemm_run_host.  N GPUs: rank g uploads rows g of N of the replicated A, the slices are
+    all-gathered over NVLink, and only this rank's B block and D block cross its PCIe link."""
+    torch, gz = cx.torch, cx.gz
+    from gemm_zoo_b200 import partition
+    bf16 = torch.bfloat16
+    phys = physical_gpu_index(cx.local_rank)
+    ha = partition.pin_near_gpu((M, K), bf16, phys)
+    hb = partition.pin_near_gpu((N, K), bf16, phys)
+    hd = partition.pin_near_gpu((M, N), bf16, phys)
+    ha.copy_(A0)
+    hb.copy_(B0)
+    if cx.world == 1:
+        run = lambda _: gemm.plan.run_host(ha, hb, None, hd, 1.0, 0.0, cx.stream)
+        h2d = 2 * M * K * 2
+        how = "gz_gemm_run_host: A, then B in column blocks up, D blocks down, GEMM per block (3 streams)"
+    else:
+        pg = partition.PartitionedHostGemm(M, N * cx.world, K, gz.DT_BF16, gz.DT_BF16, cx.rank, cx.world, cx.local_rank)
+        # the global B is N*world columns; this rank's block is its own hb
+        run = lambda _: pg(ha, hb, None, hd, 1.0, 0.0, cx.stream)
+        h2d = pg.h2d_bytes
+        how = (f"each rank uploads 1/{cx.world} of A's rows and its B block; A slices all-gathered over NVLink "
+               "(NCCL) into local memory; D block down")
+    for i in range(2):
+        run(i)
+    ms, _, _ = timed_region(cx, run, steps)
+    ms_max = cx.max_over_ranks([ms])[0]
+    d2h = M * N * 2
+    flops = 2.0 * M * N * K
+    # the result the host now holds is the product: compare a few entries with the device-resident run
+    checksum = float(hd[:4, :4].float().abs().sum())
+    per_rank_ms = ms / steps
+    return {"value": cx.world * flops / (ms_max / steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_max / steps, "steps": steps,
+            "rank0_h2d_gbs": h2d / per_rank_ms / 1e6, "rank0_d2h_gbs": d2h / per_rank_ms / 1e6,
+            "aggregate_pcie_gbs": cx.world * (h2d + d2h) / (ms_max / steps) / 1e6,
+            "path": how, "result_checksum": checksum, "host_memory": "pinned, first touched on the GPU's NUMA node"}, hd
+
+
+# ------------------------------------------------------------------ single-GPU extras
 def _time_interleaved(torch, stream, fns, sets, reps=20, warm=3):
     """Median ms of each callable, reps interleaved so both see the same thermal state."""
     for f in fns:
@@ -357,55 +410,9 @@ def _time_interleaved(torch, stream, fns, sets, reps=20, warm=3):
     return out
 
 
-def sustained_compare(gz, torch, dev, stream, A, B, D, gemm, flops, seconds, nvml_index):
-    """Seconds-long back-to-back loops (the power-capped regime): TFLOP/s, median SM clock and board
-    power over the second half of each loop, own kernel then cuBLASLt, twice."""
-    import pynvml
+def compare_cublaslt(cx, A, B, D, gemm, flops):
     from gemm_zoo_b200.cublaslt import CublasLtGemm
-    pynvml.nvmlInit()
-    h = pynvml.nvmlDeviceGetHandleByIndex(nvml_index)
-    lt = CublasLtGemm(M, N, K, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR)
-
-    def loop(fn):
-        samples, stop = [], threading.Event()
-
-        def sample():
-            while not stop.is_set():
-                samples.append((pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM),
-                                pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0))
-                time.sleep(0.02)
-        th = threading.Thread(target=sample, daemon=True)
-        th.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        n, t0 = 0, time.time()
-        e0.record(stream)
-        while time.time() - t0 < seconds:
-            for _ in range(100):
-                fn(n % len(A))
-                n += 1
-            torch.cuda.synchronize()
-        e1.record(stream)
-        torch.cuda.synchronize()
-        stop.set()
-        th.join()
-        ms = e0.elapsed_time(e1) / n
-        half = samples[len(samples) // 2:] or [(0, 0.0)]
-        clk = sorted(x[0] for x in half)[len(half) // 2]
-        pw = sorted(x[1] for x in half)[len(half) // 2]
-        return {"tflops": flops / ms / 1e9, "ms": ms, "sm_mhz": clk, "watts": pw}
-
-    out = {"seconds_each": seconds, "own": [], "cublaslt": []}
-    for _ in range(2):
-        out["own"].append(loop(lambda i: gemm(A[i], B[i], None, D, 1.0, 0.0, stream)))
-        time.sleep(1.0)
-        out["cublaslt"].append(loop(lambda i: lt(A[i], B[i], None, D, 1.0, 0.0, stream)))
-        time.sleep(1.0)
-    lt.destroy()
-    return out
-
-
-def compare_cublaslt(gz, torch, dev, stream, A, B, D, gemm, flops):
-    from gemm_zoo_b200.cublaslt import CublasLtGemm
+    torch, gz, stream = cx.torch, cx.gz, cx.stream
     lt = CublasLtGemm(M, N, K, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR)
     best_ms, best_idx = None, 0
     for idx in range(min(lt.num_algos, 6)):
@@ -421,57 +428,391 @@ def compare_cublaslt(gz, torch, dev, stream, A, B, D, gemm, flops):
         torch, stream,
         [lambda i: gemm(A[i], B[i], None, D, 1.0, 0.0, stream), lambda i: lt(A[i], B[i], None, D, 1.0, 0.0, stream)],
         len(A))
-    lt.destroy()
-    return {"value": flops / lt_ms / 1e9, "unit": "TFLOP/s", "own_interleaved": flops / own_ms / 1e9,
-            "ratio_own_over_cublaslt": lt_ms / own_ms, "algo_index": best_idx, "candidates": lt.num_algos}
+    return lt, {"value": flops / lt_ms / 1e9, "unit": "TFLOP/s", "own_interleaved": flops / own_ms / 1e9,
+                "ratio_own_over_cublaslt": lt_ms / own_ms, "algo_index": best_idx, "candidates": lt.num_algos}
 
 
-def other_dtypes(gz, torch, dev, stream):
-    """The remaining BASELINE configurations, own kernel and cuBLASLt interleaved."""
-    from gemm_zoo_b200.cublaslt import CublasLtGemm
-    res = {}
-    cases = [
-        ("fp16_8192", gz.DT_F16, gz.DT_F16, torch.float16, torch.float16, 8192, gz.COL_MAJOR, 1.0, 0.0),
-        ("tf32_8192_rowrow", gz.DT_F32, gz.DT_F32, torch.float32, torch.float32, 8192, gz.ROW_MAJOR, 1.0, 0.0),
-        ("s8_8192", gz.DT_S8, gz.DT_S32, torch.int8, torch.int32, 8192, gz.COL_MAJOR, 1, 0),
-        ("bf16_4096_beta0.5", gz.DT_BF16, gz.DT_BF16, torch.bfloat16, torch.bfloat16, 4096, gz.COL_MAJOR, 1.0, 0.5),
-        ("e4m3_8192_bf16out", gz.DT_E4M3, gz.DT_BF16, torch.float8_e4m3fn, torch.bfloat16, 8192, gz.COL_MAJOR, 1.0, 0.0),
+def sustained_compare(cx, A, B, D, gemm, lt, flops, seconds, sampler):
+    """Seconds-long back-to-back loops (the power-capped regime): TFLOP/s, median SM clock and
+    board power over the second half of each loop, cuBLASLt then the own kernel."""
+    torch, stream = cx.torch, cx.stream
+
+    def loop(fn):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n, t0 = 0, time.perf_counter()
+        e0.record(stream)
+        while time.perf_counter() - t0 < seconds:
+            for _ in range(100):
+                fn(n % len(A))
+                n += 1
+            torch.cuda.synchronize()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        ms = e0.elapsed_time(e1) / n
+        mid = t0 + (t1 - t0) / 2
+        return {"tflops": flops / ms / 1e9, "ms": ms, "launches": n, "sm_mhz": sampler.median_mhz(mid, t1),
+                "watts": sampler.median_watts(mid, t1)}
+
+    out = {"seconds_each": seconds}
+    if lt is not None:
+        out["cublaslt"] = loop(lambda i: lt(A[i], B[i], None, D, 1.0, 0.0, stream))
+        time.sleep(0.5)
+    out["own"] = loop(lambda i: gemm(A[i], B[i], None, D, 1.0, 0.0, stream))
+    if lt is not None:
+        out["ratio_own_over_cublaslt"] = out["own"]["tflops"] / out["cublaslt"]["tflops"]
+    return out
+
+
+# name, in, out, m, n, k, B column-major, alpha, beta, fill of A (dist, scale), fill of B (dist, scale)
+def config_table(gz):
+    return [
+        ("c1_fp16_1024", gz.DT_F16, gz.DT_F16, 1024, 1024, 1024, True, 1, 0, (0, 1.0), (0, 1.0)),
+        ("c5_bf16_m1", gz.DT_BF16, gz.DT_BF16, 1, 14336, 4096, True, 1, 0, (1, 1.0), (1, 0.02)),
+        ("c5_bf16_m16", gz.DT_BF16, gz.DT_BF16, 16, 14336, 4096, True, 1, 0, (1, 1.0), (1, 0.02)),
+        ("c5_bf16_m128", gz.DT_BF16, gz.DT_BF16, 128, 14336, 4096, True, 1, 0, (1, 1.0), (1, 0.02)),
+        ("c2_bf16_4096_beta", gz.DT_BF16, gz.DT_BF16, 4096, 4096, 4096, True, 1, 0.5, (1, 4096 ** -0.5), (1, 4096 ** -0.5)),
+        ("c5_bf16_m2048", gz.DT_BF16, gz.DT_BF16, 2048, 14336, 4096, True, 1, 0, (1, 1.0), (1, 0.02)),
+        ("headline_bf16_8192", gz.DT_BF16, gz.DT_BF16, 8192, 8192, 8192, True, 1, 0, (1, 1.0), (1, 8192 ** -0.5)),
+        ("fp16_8192", gz.DT_F16, gz.DT_F16, 8192, 8192, 8192, True, 1, 0, (1, 1.0), (1, 8192 ** -0.5)),
+        ("c3_tf32_8192", gz.DT_F32, gz.DT_F32, 8192, 8192, 8192, False, 1, 0, (0, 1.0), (0, 1.0)),
+        ("c4_s8_8192", gz.DT_S8, gz.DT_S32, 8192, 8192, 8192, True, 1, 0, (2, 1.0), (2, 1.0)),
+        ("c5_bf16_m16384", gz.DT_BF16, gz.DT_BF16, 16384, 14336, 4096, True, 1, 0, (1, 1.0), (1, 0.02)),
+        ("c5_bf16_16384_cube", gz.DT_BF16, gz.DT_BF16, 16384, 16384, 16384, True, 1, 0, (1, 1.0), (1, 1.0 / 128)),
+        ("next_e4m3_8192_bf16out", gz.DT_E4M3, gz.DT_BF16, 8192, 8192, 8192, True, 1, 0, (1, 1.0), (1, 8192 ** -0.5)),
     ]
-    for name, it, ot, tin, tout, sz, lb, alpha, beta in cases:
-        sets = 2 if sz == 8192 else 4
-        a = [torch.empty(sz, sz, dtype=tin, device=dev) for _ in range(sets)]
-        b = [torch.empty(sz, sz, dtype=tin, device=dev) for _ in range(sets)]
-        c = torch.empty(sz, sz, dtype=tout, device=dev)
-        d = torch.empty(sz, sz, dtype=tout, device=dev)
-        for i in range(sets):
-            if it == gz.DT_S8:
-                gz.fill(a[i], 3, 10 + i, 2)
-                gz.fill(b[i], 3, 20 + i, 2)
+
+
+def graph_time_us(torch, calls, stream, reps):
+    """Device time per launch: the launches of one pass are captured in a CUDA graph and replayed
+    between two events, so the host's launch rate (a ctypes call costs more than the small
+    configurations run) is not in the figure."""
+    with torch.cuda.stream(stream):
+        for f in calls:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for f in calls:
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * len(calls))
+
+
+def configs_leg(cx, peaks, peak_kind, reps=20):
+    """Every configuration of the specification on one GPU, own kernel beside cuBLASLt (heuristic's
+    first algorithm), alternating, better of two rounds each; operands rotate over enough sets that
+    no launch finds them in L2."""
+    from gemm_zoo_b200.cublaslt import CublasLtGemm
+    torch, gz = cx.torch, cx.gz
+    T = {gz.DT_F16: torch.float16, gz.DT_BF16: torch.bfloat16, gz.DT_F32: torch.float32, gz.DT_S8: torch.int8,
+         gz.DT_S32: torch.int32, gz.DT_E4M3: torch.float8_e4m3fn}
+    SIZE = {gz.DT_F16: 2, gz.DT_BF16: 2, gz.DT_F32: 4, gz.DT_S8: 1, gz.DT_S32: 4, gz.DT_E4M3: 1}
+    bf16_peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    hbm_peak = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    stream = torch.cuda.Stream(cx.dev)
+    table = {}
+    for (name, it, ot, m, n, k, b_col, alpha, beta, fa, fb) in config_table(gz):
+        try:
+            op_bytes = (m * k + n * k) * SIZE[it]
+            sets = 2 if op_bytes > 2 * L2_BYTES else max(1, min(8, (2 * L2_BYTES) // op_bytes + 1))
+            A = [torch.empty(m, k, dtype=T[it], device=cx.dev) for _ in range(sets)]
+            B = [torch.empty((n, k) if b_col else (k, n), dtype=T[it], device=cx.dev) for _ in range(sets)]
+            for i in range(sets):
+                gz.fill(A[i], 7, 2 * i, fa[0], fa[1])
+                gz.fill(B[i], 7, 2 * i + 1, fb[0], fb[1])
+            C = None
+            if beta:
+                C = torch.empty(m, n, dtype=T[ot], device=cx.dev)
+                gz.fill(C, 7, 99, 1, 1.0)
+            D = torch.empty(m, n, dtype=T[ot], device=cx.dev)
+            layout_b = gz.COL_MAJOR if b_col else gz.ROW_MAJOR
+            own = gz.Sm100Gemm(m, n, k, it, ot, layout_b=layout_b, device=cx.local_rank)
+            lt = CublasLtGemm(m, n, k, it, ot, layout_b=layout_b)
+            per_pass = max(sets, 4 if m * n * k < 2 ** 33 else sets)
+            own_calls = [(lambda i: (lambda: own(A[i % sets], B[i % sets], C, D, alpha, beta, stream=stream)))(i)
+                         for i in range(per_pass)]
+            lt_calls = [(lambda i: (lambda: lt(A[i % sets], B[i % sets], C, D, alpha, beta, stream=stream)))(i)
+                        for i in range(per_pass)]
+            r = reps if m * n * k < 2 ** 40 else max(3, reps // 4)
+            if m <= 128:
+                time.sleep(1.5)  # the weight-streaming shapes are sensitive to the state the last one left
+            rounds = [(graph_time_us(torch, own_calls, stream, r), graph_time_us(torch, lt_calls, stream, r))
+                      for _ in range(2)]
+            t_own = min(x[0] for x in rounds)
+            t_lt = min(x[1] for x in rounds)
+            st = own.plan.device_status(stream)[0]
+            flops = 2.0 * m * n * k
+            abytes = (m * k + n * k) * SIZE[it] + m * n * SIZE[ot] * (2 if beta else 1)
+            info = own.info()
+            e = {"m": m, "n": n, "k": k, "kernel_config": info.config, "grid": info.grid, "split_k": info.split_k,
+                 "own_us": round(t_own, 2), "cublaslt_us": round(t_lt, 2), "own_over_cublaslt": round(t_lt / t_own, 3),
+                 "own": round(flops / t_own / 1e6, 1), "cublaslt": round(flops / t_lt / 1e6, 1),
+                 "unit": "TOPS" if it == gz.DT_S8 else "TFLOP/s", "device_status": st, "operand_sets": sets}
+            if m <= 128:
+                gbs = abytes / t_own / 1e3
+                e["roofline"] = {"bound": "hbm", "achieved": round(gbs, 1), "peak": hbm_peak, "unit": "GB/s",
+                                 "frac": round(gbs / hbm_peak, 3), "peak_source": f"{peak_kind} HBM copy"}
             else:
-                gz.fill(a[i], 3, 10 + i, 1, 1.0)
-                gz.fill(b[i], 3, 20 + i, 1, sz ** -0.5)
-        gz.fill(c, 3, 30, 2 if it == gz.DT_S8 else 1, 1.0)
-        own = gz.Sm100Gemm(sz, sz, sz, it, ot, layout_b=lb, device=dev.index or 0)
-        cc = c if beta != 0 else None
-        fns = [lambda i: own(a[i], b[i], cc, d, alpha, beta, stream)]
+                scale = {gz.DT_F32: 0.5, gz.DT_S8: 2.0, gz.DT_E4M3: 2.0}.get(it, 1.0)
+                tf = flops / t_own / 1e6
+                label = f"{peak_kind} cuBLAS bf16 burst" + ("" if scale == 1.0 else f" x {scale} (nominal ratio to bf16)")
+                e["roofline"] = {"bound": "tensor", "achieved": round(tf, 1), "peak": round(bf16_peak * scale, 1),
+                                 "unit": e["unit"], "frac": round(tf / (bf16_peak * scale), 3), "peak_source": label}
+            table[name] = e
+            own.plan.destroy()
+            lt.destroy()
+            del A, B, C, D
+            torch.cuda.empty_cache()
+            time.sleep(0.5)
+        except Exception as ex:  # one configuration failing must not lose the line
+            table[name] = {"error": repr(ex)}
+    return table
+
+
+def fused_epilogue_leg(cx, reps=20):
+    """bf16 2048 x 14336 x 4096 with bias + GELU in the epilogue beside the plain GEMM."""
+    torch, gz = cx.torch, cx.gz
+    m, n, k = 2048, 14336, 4096
+    stream = torch.cuda.Stream(cx.dev)
+    sets = 2
+    A = [torch.empty(m, k, dtype=torch.bfloat16, device=cx.dev) for _ in range(sets)]
+    B = [torch.empty(n, k, dtype=torch.bfloat16, device=cx.dev) for _ in range(sets)]
+    for i in range(sets):
+        gz.fill(A[i], 8, 2 * i, 1, 1.0)
+        gz.fill(B[i], 8, 2 * i + 1, 1, 0.02)
+    bias = torch.randn(n, device=cx.dev, dtype=torch.float32)
+    D = torch.empty(m, n, dtype=torch.bfloat16, device=cx.dev)
+    g = gz.Sm100Gemm(m, n, k, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR, device=cx.local_rank)
+    plain = [(lambda i: (lambda: g(A[i], B[i], None, D, 1.0, 0.0, stream=stream)))(i) for i in range(sets)]
+    fused = [(lambda i: (lambda: g.plan.run_ex(A[i], B[i], None, D, 1.0, 0.0, bias=bias, activation=gz.ACT_GELU,
+                                                stream=stream)))(i) for i in range(sets)]
+    t_plain = min(graph_time_us(torch, plain, stream, reps) for _ in range(2))
+    t_fused = min(graph_time_us(torch, fused, stream, reps) for _ in range(2))
+    return {"workload": "bf16 2048x14336x4096, B column-major", "plain_us": round(t_plain, 2),
+            "bias_gelu_us": round(t_fused, 2), "fused_over_plain_time": round(t_fused / t_plain, 3)}
+
+
+def ksharded_leg(cx, reps=20):
+    """K-sharded GEMM (rank g holds A[:, K_g], B[K_g, :]) with the reduce-scatter fused into the
+    epilogue (peer stores over NVLink), beside the GEMM + NCCL reduce-scatter route; both routes
+    are compared with each other (they add the ranks' partial sums in different orders)."""
+    torch, gz, dist = cx.torch, cx.gz, cx.dist
+    from gemm_zoo_b200.ksharded import KShardedGemm
+    m, n, k_local = 4096, 8192, 4096
+    cols = n // cx.world
+    a = torch.empty(m, k_local, dtype=torch.bfloat16, device=cx.dev)
+    b = torch.empty(n, k_local, dtype=torch.bfloat16, device=cx.dev)  # column-major K x N slice
+    gz.fill(a, 31 + cx.rank, 0, 1, 1.0)
+    gz.fill(b, 31 + cx.rank, 1, 1, 0.02)
+    d_fused = torch.empty(m, cols, dtype=torch.bfloat16, device=cx.dev)
+    fused = KShardedGemm(m, n, k_local, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR)
+    for _ in range(3):
+        fused(a, b, None, d_fused, 1, 0, cx.stream)
+    ms, _, _ = timed_region(cx, lambda i: fused(a, b, None, d_fused, 1, 0, cx.stream), reps)
+    fused_ms = cx.max_over_ranks([ms])[0] / reps
+    st = fused.plan.status(cx.stream)[0]
+    # comparison route: fp32 partial product, transposing copy into column blocks, ncclReduceScatter, cast
+    part = torch.empty(m, n, dtype=torch.float32, device=cx.dev)
+    blocks = torch.empty(cx.world, m, cols, dtype=torch.float32, device=cx.dev)
+    mine = torch.empty(m, cols, dtype=torch.float32, device=cx.dev)
+    d_lib = torch.empty_like(d_fused)
+    g = gz.Sm100Gemm(m, n, k_local, gz.DT_BF16, gz.DT_F32, layout_b=gz.COL_MAJOR, device=cx.local_rank)
+
+    def library_route(_):
+        g(a, b, None, part, 1.0, 0.0, cx.stream)
+        blocks.copy_(part.view(m, cx.world, cols).permute(1, 0, 2))
+        dist.reduce_scatter_tensor(mine, blocks)
+        d_lib.copy_(mine)
+
+    for _ in range(3):
+        library_route(0)
+    ms2, _, _ = timed_region(cx, library_route, reps)
+    nccl_ms = cx.max_over_ranks([ms2])[0] / reps
+    err = float((d_fused.float() - d_lib.float()).abs().max() / d_lib.float().abs().max())
+    err = cx.max_over_ranks([err])[0]
+    fused.close()
+    flops = 2.0 * m * n * k_local
+    link_bytes = m * n * 4 * (cx.world - 1) / cx.world
+    floor_ms = max(flops / 1.6e15, link_bytes / 770e9) * 1e3
+    return {"workload": f"bf16 {m}x{n}x{k_local} per rank, K sharded over {cx.world} GPUs", "fused_us": round(fused_ms * 1e3, 1),
+            "gemm_plus_nccl_us": round(nccl_ms * 1e3, 1), "speedup": round(nccl_ms / fused_ms, 2),
+            "roofline_us": round(floor_ms * 1e3, 1), "frac": round(floor_ms / fused_ms, 3), "device_status": st,
+            "max_abs_diff_over_max_abs_between_routes": round(err, 5)}
+
+
+# ------------------------------------------------------------------ main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=10, help="how many times the timed region of --steps steps is measured")
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--no-extras", action="store_true",
+                    help="headline leg, partitioned leg and end-to-end leg only (same as --extras none)")
+    ap.add_argument("--extras", default="all",
+                    help="comma list of the optional legs: cublaslt,sustained,configs,fused,cpu,ksharded; all; none")
+    ap.add_argument("--sustain", type=float, default=2.0,
+                    help="seconds each of the seconds-long own / cuBLASLt loops (0 = skip)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "own" else args.warmup
+    all_extras = {"cublaslt", "sustained", "configs", "fused", "cpu", "ksharded"}
+    extras = set() if (args.no_extras or args.extras == "none") else (
+        all_extras if args.extras == "all" else set(args.extras.split(",")) & all_extras)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import gemm_zoo_b200 as gz
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists for the product path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    gz.lib()  # fail loudly if the extension is missing
+    stream = torch.cuda.current_stream(dev)
+    cx = Ctx(torch, dist, gz, dev, stream, rank, world, local_rank)
+
+    SETS = 3
+    bf16 = torch.bfloat16
+    A = [torch.empty(M, K, dtype=bf16, device=dev) for _ in range(SETS)]
+    B = [torch.empty(N, K, dtype=bf16, device=dev) for _ in range(SETS)]  # column-major K x N
+    D = torch.empty(M, N, dtype=bf16, device=dev)
+    for i in range(SETS):
+        # A is replicated across ranks (same seed); each rank owns its own column block of B.
+        gz.fill(A[i], 1000 + i, 1, 1, 1.0)
+        gz.fill(B[i], 2000 + i, 2 + rank, 1, K ** -0.5)
+    gemm = gz.Sm100Gemm(M, N, K, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR, device=local_rank)
+    info = gemm.info()
+    flops = 2.0 * M * N * K
+
+    def step(i):
+        gemm(A[i % SETS], B[i % SETS], None, D, 1.0, 0.0, stream)
+
+    # ---- headline: `repeats` timed regions of `steps` steps
+    for i in range(args.warmup):
+        step(i)
+    cx.barrier()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    regions = [timed_region(cx, step, args.steps) for _ in range(max(1, args.repeats))]
+    t_head_end = time.perf_counter()
+    status, detail = gemm.plan.device_status(stream)
+    if status != 0:
+        raise SystemExit(f"device status {status} {detail}")
+    ms_max = cx.max_over_ranks([r[0] for r in regions])
+    order = sorted(range(len(ms_max)), key=lambda i: ms_max[i])
+    med = order[len(order) // 2]
+    ms_per_step = ms_max[med] / args.steps
+    value = world * flops / (ms_per_step * 1e-3) / 1e12
+    tf_of = lambda ms: world * flops / (ms / args.steps * 1e-3) / 1e12
+    rep_mhz = [sampler.median_mhz(r[1], r[2]) for r in regions]
+    repeats = {"n": len(regions), "tflops_median": value, "tflops_min": tf_of(max(ms_max)), "tflops_max": tf_of(min(ms_max)),
+               "tflops": [round(tf_of(x), 1) for x in ms_max], "rank0_sm_mhz": rep_mhz,
+               # time x clock: constant when the spread between repeats (and chips) is clock alone
+               "rank0_ms_per_step_x_ghz": [round(regions[i][0] / args.steps * (rep_mhz[i] or 0) / 1e3, 4) for i in range(len(regions))]}
+    head_clocks = {"sm_mhz": sampler.median_mhz(regions[0][1], t_head_end), "sm_max_mhz": sampler.max_mhz}
+
+    # ---- the column-partitioned configuration (strong scaling) and the end-to-end leg
+    part = partitioned_leg(cx, steps=max(3, min(args.steps, 10)), warmup=3)
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e, hd = e2e_leg(cx, gemm, A[0], B[0], e2e_steps)
+    # the host result of the end-to-end leg against the device-resident run on the same operands
+    step(0)
+    torch.cuda.synchronize(dev)
+    e2e["matches_device_run"] = cx.all_ok(bool(torch.equal(hd.view(torch.int16), D.cpu().view(torch.int16))))
+
+    peaks, peak_kind = load_peaks()
+    peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    achieved = flops / (regions[med][0] / args.steps * 1e-3) / 1e12  # this rank's kernel, the median repeat
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": config_dict(world),
+        "kernel": {"config": info.config, "tile": [info.tile_m, info.tile_n, info.tile_k], "stages": info.stages,
+                   "ctas_per_tile": info.ctas_per_tile, "grid": info.grid, "epilogue_tma": info.epilogue_tma},
+        "repeats": repeats,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
+                     "frac": achieved / peak_tf,
+                     "traffic": committed_traffic(info.config, M, N, K, "bf16", "bf16"),
+                     "peak_source": f"{peak_kind} cuBLAS bf16 burst", "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS,
+                     "algorithmic_flops_per_launch": flops, "algorithmic_bytes_per_launch": 3 * M * N * 2},
+        "partitioned": part,
+        "e2e": e2e,
+        "gpu_launches": args.steps,
+    }
+
+    if rank == 0 and world == 1 and extras & {"cublaslt", "sustained"}:
         lt = None
         try:
-            lt = CublasLtGemm(sz, sz, sz, it, ot, layout_b=lb)
-            fns.append(lambda i: lt(a[i], b[i], cc, d, alpha, beta, stream))
-        except Exception:
-            lt = None
-        ms = _time_interleaved(torch, stream, fns, sets, reps=10)
-        fl = 2.0 * sz ** 3
-        entry = {"own": fl / ms[0] / 1e9, "unit": "TOPS" if it == gz.DT_S8 else "TFLOP/s",
-                 "config": own.info().config}
+            lt, line["cublaslt"] = compare_cublaslt(cx, A, B, D, gemm, flops)
+        except Exception as e:  # the comparator is optional equipment
+            line["cublaslt"] = {"error": repr(e)}
+        if args.sustain > 0 and "sustained" in extras:
+            try:
+                sus = sustained_compare(cx, A, B, D, gemm, lt, flops, args.sustain, sampler)
+                line["sustained"] = sus
+                sus_peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+                line["roofline_sustained"] = {"bound": "tensor", "achieved": sus["own"]["tflops"], "peak": sus_peak,
+                                              "unit": "TFLOP/s", "frac": sus["own"]["tflops"] / sus_peak,
+                                              "peak_source": f"{peak_kind} cuBLAS bf16, seconds-long loop under the power cap",
+                                              "sm_mhz": sus["own"]["sm_mhz"], "watts": sus["own"]["watts"]}
+            except Exception as e:
+                line["sustained"] = {"error": repr(e)}
         if lt is not None:
-            entry["cublaslt"] = fl / ms[1] / 1e9
             lt.destroy()
-        res[name] = entry
-        own.plan.destroy()
-        del a, b, c, d
-        torch.cuda.empty_cache()
-    return res
+    clocks = sampler.stop()
+    clocks.update(headline_sm_mhz=head_clocks["sm_mhz"])
+    line["clocks"] = clocks
+    del A, B, D
+    torch.cuda.empty_cache()
+    line["cpu_baseline"] = None
+    if rank == 0 and world == 1:
+        time.sleep(1.0)
+        if "configs" in extras:
+            try:
+                line["configs"] = configs_leg(cx, peaks, peak_kind)
+            except Exception as e:
+                line["configs"] = {"error": repr(e)}
+        if "fused" in extras:
+            try:
+                line["fused_epilogue"] = fused_epilogue_leg(cx)
+            except Exception as e:
+                line["fused_epilogue"] = {"error": repr(e)}
+        if "cpu" in extras:
+            rows = 2048 if (os.cpu_count() or 1) >= 32 else 512
+            tf, dt, cores = cpu_reference_tflops(rows)
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": f"{rows} of {M} rows of A (all columns, full K), {dt:.1f} s, fp64 accumulation"}
+    if world > 1 and "ksharded" in extras:
+        try:
+            line["ksharded"] = ksharded_leg(cx)
+        except Exception as e:
+            line["ksharded"] = {"error": repr(e)}
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":

@@ -18,6 +18,7 @@ CFG_2CTA_M512_N256 = 10
 FLAG_EPILOGUE_DIRECT, FLAG_EPILOGUE_TMA, FLAG_TEST_WITHHOLD_ACC_READY = 0x1, 0x2, 0x80000000
 FLAG_NO_SPLIT_K, FLAG_SPLIT_K = 0x4, 0x8
 FLAG_BROADCAST_A, FLAG_BROADCAST_B = 0x10, 0x20
+HOST_A_ON_DEVICE = 0x1
 
 GZ_OK = 0
 GZ_ERR_INVALID_ARG, GZ_ERR_UNSUPPORTED, GZ_ERR_MISALIGNED, GZ_ERR_CUDA = 1, 2, 3, 4
@@ -27,7 +28,8 @@ GZ_ERR_DEVICE_TIMEOUT, GZ_ERR_NO_DEVICE, GZ_ERR_TOO_LARGE, GZ_ERR_OUT_OF_MEMORY 
 EXPORTED_SYMBOLS = [
     "gz_gemm_desc_validate", "gz_gemm_plan_create", "gz_gemm_plan_destroy", "gz_gemm_plan_info",
     "gz_gemm_plan_set_profile",
-    "gz_gemm_run", "gz_gemm_run_ex", "gz_gemm_run_host", "gz_gemm_skinny_static", "gz_last_device_status", "gz_status_string",
+    "gz_gemm_run", "gz_gemm_run_ex", "gz_gemm_run_host", "gz_gemm_run_host_ex", "gz_gemm_skinny_static", "gz_static_last_device_status",
+    "gz_last_device_status", "gz_status_string",
     "gz_last_cuda_error", "gz_fill", "gz_tile_coords", "gz_partition_columns", "gz_version",
 ]
 
@@ -134,8 +136,12 @@ def lib():
     L.gz_gemm_plan_set_profile.restype = C.c_int
     L.gz_gemm_run_host.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp]
     L.gz_gemm_run_host.restype = C.c_int
+    L.gz_gemm_run_host_ex.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, u32]
+    L.gz_gemm_run_host_ex.restype = C.c_int
     L.gz_gemm_skinny_static.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, vp]
     L.gz_gemm_skinny_static.restype = C.c_int
+    L.gz_static_last_device_status.argtypes = [i32, vp, C.POINTER(u32 * 4)]
+    L.gz_static_last_device_status.restype = C.c_int
     L.gz_last_device_status.argtypes = [vp, vp, C.POINTER(u32 * 4)]
     L.gz_last_device_status.restype = C.c_int
     L.gz_status_string.argtypes = [C.c_int]
@@ -243,16 +249,27 @@ class Plan:
         if st != GZ_OK:
             raise GzError(st, "gz_gemm_run_ex")
 
-    def run_host(self, a, b, c, d, alpha, beta, stream=None):
+    def run_host(self, a, b, c, d, alpha, beta, stream=None, a_on_device=False):
+        """Host operands (gz_gemm_run_host).  a_on_device: `a` is already in this GPU's memory
+        (gz_gemm_run_host_ex with GZ_HOST_A_ON_DEVICE); b, c, d stay host pointers."""
         al, be = (_scalar(self.desc.in_type, alpha, self.desc.out_type),
                   _scalar(self.desc.in_type, beta, self.desc.out_type))
-        st = lib().gz_gemm_run_host(self._h, _ptr(a), _ptr(b), _ptr(c), _ptr(d), C.byref(al),
-                                    C.byref(be), _stream_handle(stream))
+        st = lib().gz_gemm_run_host_ex(self._h, _ptr(a), _ptr(b), _ptr(c), _ptr(d), C.byref(al),
+                                       C.byref(be), _stream_handle(stream), HOST_A_ON_DEVICE if a_on_device else 0)
         if st != GZ_OK:
             raise GzError(st, "gz_gemm_run_host")
 
     def set_profile(self, buf):
-        """buf: torch int64 CUDA tensor of 8 * info().grid words, or None."""
+        """buf: contiguous torch int64 CUDA tensor of at least 16 * info().grid words (the kernel
+        writes 16 words per CTA), or None to switch the counters off."""
+        if buf is not None:
+            import torch
+            need = 16 * self.info().grid
+            if not (isinstance(buf, torch.Tensor) and buf.is_cuda and buf.dtype == torch.int64 and
+                    buf.is_contiguous() and buf.numel() >= need):
+                raise ValueError(f"set_profile needs a contiguous int64 CUDA tensor of at least {need} words")
+            if buf.device.index != self.desc.device:
+                raise ValueError("set_profile: the buffer must live on the plan's device")
         st = lib().gz_gemm_plan_set_profile(self._h, _ptr(buf))
         if st != GZ_OK:
             raise GzError(st, "gz_gemm_plan_set_profile")
@@ -318,9 +335,17 @@ STATIC_SCRATCH_BYTES = 8 << 20
 def gemm_skinny_static(desc: GemmDesc, a, b, c, d, alpha, beta, stream=None):
     """gz_gemm_skinny_static: the skinny split-K GEMM with its scratch in the library's fixed
     array, for hosts that must not allocate.  Returns the gz_status (0 = launched)."""
-    al, be = _scalar(desc.in_type, alpha), _scalar(desc.in_type, beta)
+    al, be = _scalar(desc.in_type, alpha, desc.out_type), _scalar(desc.in_type, beta, desc.out_type)
     return lib().gz_gemm_skinny_static(C.byref(desc), _ptr(a), _ptr(b), _ptr(c), _ptr(d), C.byref(al),
                                        C.byref(be), _stream_handle(stream))
+
+
+def static_device_status(device=0, stream=None):
+    """gz_static_last_device_status: (status, detail[4]) of the gz_gemm_skinny_static launches on
+    `device` after synchronising `stream`; a recorded timeout is cleared by the read."""
+    detail = (C.c_uint32 * 4)()
+    st = lib().gz_static_last_device_status(device, _stream_handle(stream), C.byref(detail))
+    return st, list(detail)
 
 
 def fill(t, seed, stream_id, dist, scale=1.0, stream=None):

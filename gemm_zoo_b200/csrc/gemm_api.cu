@@ -21,6 +21,7 @@
 #include <string>
 
 #include "gemmzoo/gemm.h"
+#include "kernel_table.h"
 #include "rng.h"
 #include "simt_gemm.cuh"
 #include "sm100_gemm.cuh"
@@ -358,113 +359,22 @@ void fill_info(const Problem& pr, int config, int sm_count, gz_plan_info* info) 
   }
 }
 
-using LaunchFn = cudaError_t (*)(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,
-                                 const gz::GemmParams&, int grid, cudaStream_t);
-using AttrFn = cudaError_t (*)();
+using gz::KernelEntry;
+using gz::LaunchFn;
 
-template <class Cfg, bool PROF = false>
-cudaError_t set_attr() {
-  return cudaFuncSetAttribute(gz::sm100_gemm_kernel<Cfg, PROF>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-}
-
-template <class Cfg, bool PROF = false>
-cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td,
-                   const gz::GemmParams& p, int grid, cudaStream_t stream) {
-  cudaLaunchConfig_t cfg;
-  std::memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  if (Cfg::CTAS > 1) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = Cfg::CTAS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-  }
-  return cudaLaunchKernelEx(&cfg, gz::sm100_gemm_kernel<Cfg, PROF>, ta, tb, td, p);
-}
-
-struct KernelEntry {
-  LaunchFn launch;
-  AttrFn attr;
-  LaunchFn launch_prof;  // same kernel with stall counters compiled in (may be null)
-  AttrFn attr_prof;
-};
-
-template <class C, bool WITH_PROF>
-KernelEntry make_entry() {
-  if constexpr (WITH_PROF) return {launch<C>, set_attr<C>, launch<C, true>, set_attr<C, true>};
-  else return {launch<C>, set_attr<C>, nullptr, nullptr};
-}
-
-// Stall-counter variants are compiled for the bf16/fp16 -> 16-bit kernels only.
-template <gz::ptx::Kind KIND, typename TOut, bool WITH_PROF = false>
-KernelEntry entry_for_shape(int config) {
-  switch (config) {
-    case GZ_CFG_2CTA_N256: {
-      using C = gz::GemmCfg<KIND, TOut, 256, 2, 6>;
-      return make_entry<C, WITH_PROF>();
-    }
-    case GZ_CFG_1CTA_N256: {
-      using C = gz::GemmCfg<KIND, TOut, 256, 1, 4>;
-      return make_entry<C, WITH_PROF>();
-    }
-    case GZ_CFG_2CTA_N128: {
-      using C = gz::GemmCfg<KIND, TOut, 128, 2, 8>;
-      return make_entry<C, WITH_PROF>();
-    }
-    case GZ_CFG_1CTA_N128: {
-      using C = gz::GemmCfg<KIND, TOut, 128, 1, 6>;
-      return make_entry<C, WITH_PROF>();
-    }
-    case GZ_CFG_1CTA_N64: {
-      using C = gz::GemmCfg<KIND, TOut, 64, 1, 8>;
-      return make_entry<C, WITH_PROF>();
-    }
-    case GZ_CFG_SWAP_M16: {
-      using C = gz::GemmCfg<KIND, TOut, 16, 1, 12, true>;
-      return make_entry<C, WITH_PROF>();
-    }
-    case GZ_CFG_SWAP_M32: {
-      using C = gz::GemmCfg<KIND, TOut, 32, 1, 11, true>;
-      return make_entry<C, WITH_PROF>();
-    }
-    case GZ_CFG_SWAP_M64: {
-      using C = gz::GemmCfg<KIND, TOut, 64, 1, 9, true>;
-      return make_entry<C, WITH_PROF>();
-    }
-    case GZ_CFG_SWAP_M128: {
-      using C = gz::GemmCfg<KIND, TOut, 128, 1, 6, true>;
-      return make_entry<C, false>();
-    }
-    case GZ_CFG_2CTA_M512_N256: {
-      using C = gz::GemmCfg<KIND, TOut, 256, 2, 4, false, 2>;
-      return make_entry<C, WITH_PROF>();
-    }
-  }
-  return {nullptr, nullptr, nullptr, nullptr};
-}
-
+// The kernels themselves are instantiated in csrc/inst/*.cu, one translation unit per pair of types.
 KernelEntry entry_for(int in, int out, int config) {
-  using gz::ptx::Kind;
-  if (in == GZ_DT_F16 && out == GZ_DT_F16) return entry_for_shape<Kind::F16, __half>(config);
-  if (in == GZ_DT_BF16 && out == GZ_DT_BF16)
-    return entry_for_shape<Kind::F16, __nv_bfloat16, true>(config);
-  if ((in == GZ_DT_F16 || in == GZ_DT_BF16) && out == GZ_DT_F32)
-    return entry_for_shape<Kind::F16, float>(config);
-  if (in == GZ_DT_F32) return entry_for_shape<Kind::TF32, float>(config);
-  if (in == GZ_DT_S8 && out == GZ_DT_S32) return entry_for_shape<Kind::I8, int32_t>(config);
-  if (in == GZ_DT_S8 && out == GZ_DT_F16) return entry_for_shape<Kind::I8, __half>(config);
-  if (in == GZ_DT_S8 && out == GZ_DT_BF16) return entry_for_shape<Kind::I8, __nv_bfloat16>(config);
-  if (in == GZ_DT_S8 && out == GZ_DT_F32) return entry_for_shape<Kind::I8, float>(config);
-  if (is_fp8(in) && out == GZ_DT_F16) return entry_for_shape<Kind::F8, __half>(config);
-  if (is_fp8(in) && out == GZ_DT_BF16) return entry_for_shape<Kind::F8, __nv_bfloat16>(config);
-  if (is_fp8(in) && out == GZ_DT_F32) return entry_for_shape<Kind::F8, float>(config);
+  if (in == GZ_DT_F16 && out == GZ_DT_F16) return gz::kernels_f16_f16(config);
+  if (in == GZ_DT_BF16 && out == GZ_DT_BF16) return gz::kernels_bf16_bf16(config);
+  if ((in == GZ_DT_F16 || in == GZ_DT_BF16) && out == GZ_DT_F32) return gz::kernels_16_f32(config);
+  if (in == GZ_DT_F32) return gz::kernels_tf32(config);
+  if (in == GZ_DT_S8 && out == GZ_DT_S32) return gz::kernels_s8_s32(config);
+  if (in == GZ_DT_S8 && out == GZ_DT_F16) return gz::kernels_s8_f16(config);
+  if (in == GZ_DT_S8 && out == GZ_DT_BF16) return gz::kernels_s8_bf16(config);
+  if (in == GZ_DT_S8 && out == GZ_DT_F32) return gz::kernels_s8_f32(config);
+  if (is_fp8(in) && out == GZ_DT_F16) return gz::kernels_f8_f16(config);
+  if (is_fp8(in) && out == GZ_DT_BF16) return gz::kernels_f8_bf16(config);
+  if (is_fp8(in) && out == GZ_DT_F32) return gz::kernels_f8_f32(config);
   return {nullptr, nullptr, nullptr, nullptr};
 }
 
@@ -795,12 +705,6 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
     p.test_flags = (pr.d.flags & 0x80000000u) ? 1u : 0u;
     // Skinny problems stream the weight matrix once: spread the tiles' K positions over the HBM channels.
     if (pr.d.m <= 128) p.tune |= gz::TUNE_K_STAGGER;
-    // Developer tuning knobs, read once per plan.
-    if (const char* e = std::getenv("GZ_TUNE")) p.tune = (uint32_t)std::strtoul(e, nullptr, 0);
-    if (const char* e = std::getenv("GZ_TUNE_GROUP_M")) {
-      const long g = std::strtol(e, nullptr, 0);
-      if (g > 0) p.grid.group_m = (uint32_t)g;
-    }
     p.ldc = pr.d.ldc;
     p.ldd = pr.d.ldd;
     p.status = pl->status_dev;
@@ -1031,8 +935,14 @@ GZ_API gz_status gz_gemm_run_ex(gz_plan* pl, const void* a, const void* b, const
   return run_impl(pl, a, b, c, d, alpha, beta, stream_v, nullptr, ep);
 }
 
-GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, const void* c, void* d,
-                                  const void* alpha, const void* beta, void* stream_v) {
+}  // extern "C"
+
+namespace {
+
+// a_on_device: A is a device pointer on the plan's GPU and already valid in stream order (the
+// replicated operand of a column-partitioned run, gathered GPU to GPU); only B, C and D cross PCIe.
+gz_status run_host_impl(gz_plan* pl, const void* a, const void* b, const void* c, void* d, const void* alpha,
+                        const void* beta, void* stream_v, bool a_on_device) {
   if (!pl || !a || !b || !d) return GZ_ERR_INVALID_ARG;
   const Problem& pr = pl->pr;
   float af, bf;
@@ -1054,9 +964,9 @@ GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, con
   const size_t d_bytes = (size_t)pr.d.m * pr.d.ldd * pr.out_size;
   {
     std::lock_guard<std::mutex> lock(pl->mu);
-    if (!pl->ha) {
+    if (!pl->hb) {
       const size_t cd = c_bytes > d_bytes ? c_bytes : d_bytes;
-      if (!cuda_ok(cudaMalloc(&pl->ha, a_bytes), "cudaMalloc(A staging)") ||
+      if ((!a_on_device && !cuda_ok(cudaMalloc(&pl->ha, a_bytes), "cudaMalloc(A staging)")) ||
           !cuda_ok(cudaMalloc(&pl->hb, b_bytes), "cudaMalloc(B staging)") ||
           !cuda_ok(cudaMalloc(&pl->hc, cd), "cudaMalloc(C staging)") ||
           !cuda_ok(cudaMalloc(&pl->hd, cd), "cudaMalloc(D staging)"))
@@ -1065,14 +975,19 @@ GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, con
   }
   // Small problems: one upload, one launch, one download on the caller's stream.
   const bool pipelined = (a_bytes + b_bytes + d_bytes >= (size_t(32) << 20)) && pr.d.n >= 2048;
+  if (!a_on_device && !pl->ha) {  // a plan first used with a resident A, now with a host A
+    std::lock_guard<std::mutex> lock(pl->mu);
+    if (!pl->ha && !cuda_ok(cudaMalloc(&pl->ha, a_bytes), "cudaMalloc(A staging)")) return GZ_ERR_OUT_OF_MEMORY;
+  }
+  const void* a_dev = a_on_device ? a : pl->ha;
   if (!pipelined) {
-    if (!cuda_ok(cudaMemcpyAsync(pl->ha, a, a_bytes, cudaMemcpyHostToDevice, stream), "H2D A") ||
+    if ((!a_on_device && !cuda_ok(cudaMemcpyAsync(pl->ha, a, a_bytes, cudaMemcpyHostToDevice, stream), "H2D A")) ||
         !cuda_ok(cudaMemcpyAsync(pl->hb, b, b_bytes, cudaMemcpyHostToDevice, stream), "H2D B"))
       return GZ_ERR_CUDA;
     if (!beta_zero &&
         !cuda_ok(cudaMemcpyAsync(pl->hc, c, c_bytes, cudaMemcpyHostToDevice, stream), "H2D C"))
       return GZ_ERR_CUDA;
-    st = gz_gemm_run(pl, pl->ha, pl->hb, beta_zero ? nullptr : pl->hc, pl->hd, alpha, beta, stream_v);
+    st = gz_gemm_run(pl, a_dev, pl->hb, beta_zero ? nullptr : pl->hc, pl->hd, alpha, beta, stream_v);
     if (st != GZ_OK) return st;
     if (!cuda_ok(cudaMemcpyAsync(d, pl->hd, d_bytes, cudaMemcpyDeviceToHost, stream), "D2H D") ||
         !cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize"))
@@ -1118,10 +1033,13 @@ GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, con
   }
   const int64_t cols = pl->block_cols;
   const size_t isz = pr.in_size, osz = pr.out_size;
+  // With a host A the uploads start where the caller's stream stands.  With a resident A the
+  // caller's stream may still be waiting for A to be gathered; the uploads of B must not wait for
+  // that too (the previous call returned with both copy streams idle, so nothing else orders them).
   bool ok = cuda_ok(cudaEventRecord(pl->ev_start, stream), "cudaEventRecord") &&
-            cuda_ok(cudaStreamWaitEvent(pl->copy_in, pl->ev_start, 0), "cudaStreamWaitEvent") &&
+            (a_on_device || cuda_ok(cudaStreamWaitEvent(pl->copy_in, pl->ev_start, 0), "cudaStreamWaitEvent")) &&
             cuda_ok(cudaStreamWaitEvent(pl->copy_out, pl->ev_start, 0), "cudaStreamWaitEvent") &&
-            cuda_ok(cudaMemcpyAsync(pl->ha, a, a_bytes, cudaMemcpyHostToDevice, pl->copy_in), "H2D A");
+            (a_on_device || cuda_ok(cudaMemcpyAsync(pl->ha, a, a_bytes, cudaMemcpyHostToDevice, pl->copy_in), "H2D A"));
   for (int j = 0; ok && j < pl->blocks; ++j) {
     const int64_t n0 = (int64_t)j * cols;
     const int64_t nj = (n0 + cols <= pr.d.n) ? cols : pr.d.n - n0;
@@ -1152,7 +1070,7 @@ GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, con
     const char* cj = static_cast<const char*>(pl->hc) + (size_t)n0 * osz;
     char* dj = static_cast<char*>(pl->hd) + (size_t)n0 * osz;
     if (!cuda_ok(cudaStreamWaitEvent(stream, pl->ev_in[j], 0), "cudaStreamWaitEvent")) return GZ_ERR_CUDA;
-    st = gz_gemm_run(sub, pl->ha, bj, beta_zero ? nullptr : cj, dj, alpha, beta, stream_v);
+    st = gz_gemm_run(sub, a_dev, bj, beta_zero ? nullptr : cj, dj, alpha, beta, stream_v);
     if (st != GZ_OK) return st;
     const size_t pitch_h = (size_t)pr.d.ldd * osz;
     if (!cuda_ok(cudaEventRecord(pl->ev_gemm[j], stream), "cudaEventRecord") ||
@@ -1168,6 +1086,21 @@ GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, con
   return GZ_OK;
 }
 
+}  // namespace
+
+extern "C" {
+
+GZ_API gz_status gz_gemm_run_host(gz_plan* pl, const void* a, const void* b, const void* c, void* d,
+                                  const void* alpha, const void* beta, void* stream_v) {
+  return run_host_impl(pl, a, b, c, d, alpha, beta, stream_v, false);
+}
+
+GZ_API gz_status gz_gemm_run_host_ex(gz_plan* pl, const void* a, const void* b, const void* c, void* d,
+                                     const void* alpha, const void* beta, void* stream_v, uint32_t host_flags) {
+  if (host_flags & ~GZ_HOST_A_ON_DEVICE) return GZ_ERR_INVALID_ARG;
+  return run_host_impl(pl, a, b, c, d, alpha, beta, stream_v, (host_flags & GZ_HOST_A_ON_DEVICE) != 0);
+}
+
 GZ_API gz_status gz_last_device_status(gz_plan* pl, void* stream_v, uint32_t detail[4]) {
   if (!pl) return GZ_ERR_INVALID_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
@@ -1180,6 +1113,12 @@ GZ_API gz_status gz_last_device_status(gz_plan* pl, void* stream_v, uint32_t det
   if (detail) std::memcpy(detail, h, sizeof(h));
   if (h[0] != 0) {
     (void)cudaMemset(pl->status_dev, 0, sizeof(h));
+    // A split-K launch that gave up may have left arrival counters of unfinished tiles non-zero
+    // (only a tile's last arriver resets its counter); the next launch must find them at zero.
+    if (pl->base.split_k && pl->base.counters) {
+      const size_t counter_bytes = (size_t)pl->base.grid.num_tiles * (size_t)pl->pr.d.batch * 4;
+      (void)cudaMemset(pl->base.counters, 0, counter_bytes);
+    }
     return GZ_ERR_DEVICE_TIMEOUT;
   }
   return GZ_OK;
@@ -1414,6 +1353,7 @@ extern "C" GZ_API gz_status gz_gemm_skinny_static(const gz_gemm_desc* desc, cons
   p.ldc = pr.d.ldc;
   p.ldd = pr.d.ldd;
   p.tune = gz::TUNE_K_STAGGER;  // as gz_gemm_plan_create does for skinny problems (same summation order)
+  p.test_flags = (pr.d.flags & GZ_FLAG_TEST_WITHHOLD_ACC_READY) ? 1u : 0u;
   p.wait_limit_ns = pr.d.wait_limit_ns;
   p.alpha_f = af;
   p.beta_f = bf;
@@ -1429,9 +1369,11 @@ extern "C" GZ_API gz_status gz_gemm_skinny_static(const gz_gemm_desc* desc, cons
   p.counters = reinterpret_cast<int*>(base + (ws_bytes - counter_bytes));
   p.status = reinterpret_cast<uint32_t*>(base + (GZ_STATIC_SCRATCH_BYTES - kStatusBytes));
   // The array keeps whatever the last call left in it.  The partial sums are always written before
-  // they are read; the arrival counters and the status words must start at zero.
-  if (!cuda_ok(cudaMemsetAsync(p.counters, 0, counter_bytes, stream), "clear arrival counters") ||
-      !cuda_ok(cudaMemsetAsync(p.status, 0, kStatusBytes, stream), "clear status words"))
+  // they are read; the arrival counters must start at zero (a launch that gave up on a bounded wait
+  // may have left some behind).  The status words are NOT cleared here: they start at zero when the
+  // library image is loaded, keep the first failure until gz_static_last_device_status reads (and
+  // clears) them, so a timeout cannot be lost under the next call.
+  if (!cuda_ok(cudaMemsetAsync(p.counters, 0, counter_bytes, stream), "clear arrival counters"))
     return GZ_ERR_CUDA;
 
   CUtensorMap ta, tb;
@@ -1448,6 +1390,27 @@ extern "C" GZ_API gz_status gz_gemm_skinny_static(const gz_gemm_desc* desc, cons
       !encode_input(&tb, a, pr.a_mn_major, pr.d.m, pr.d.lda, p.b))
     return GZ_ERR_CUDA;
   if (!cuda_ok(entry.launch(ta, tb, ta, p, info.grid, stream), "kernel launch")) return GZ_ERR_CUDA;
+  return GZ_OK;
+}
+
+extern "C" GZ_API gz_status gz_static_last_device_status(int32_t device, void* stream_v, uint32_t detail[4]) {
+  StaticScratchDevice* sd = nullptr;
+  gz_status st = static_scratch_setup(device, &sd);
+  if (st != GZ_OK) return st;
+  DeviceGuard guard(device);
+  if (!guard.ok()) return GZ_ERR_CUDA;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  constexpr size_t kStatusBytes = 256;
+  unsigned char* words = static_cast<unsigned char*>(sd->ptr) + (GZ_STATIC_SCRATCH_BYTES - kStatusBytes);
+  uint32_t h[4] = {0, 0, 0, 0};
+  if (!cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize") ||
+      !cuda_ok(cudaMemcpy(h, words, sizeof(h), cudaMemcpyDeviceToHost), "read status"))
+    return GZ_ERR_CUDA;
+  if (detail) std::memcpy(detail, h, sizeof(h));
+  if (h[0] != 0) {
+    (void)cudaMemset(words, 0, sizeof(h));
+    return GZ_ERR_DEVICE_TIMEOUT;
+  }
   return GZ_OK;
 }
 

@@ -127,7 +127,7 @@ struct GemmParams {
   const float* bias;
   const float* row_scale;
   const float* col_scale;
-  // Tuning switches (see TUNE_* below).
+  // Scheduling switches set by the plan (see TUNE_* below).
   uint32_t tune;
   // Optional stall counters, 16 words per CTA (null = off):
   //  [0] A producer: clocks waiting for a free stage   [1] A producer: total clocks
@@ -145,7 +145,6 @@ struct GemmParams {
 };
 
 enum : uint32_t {
-  TUNE_COMMIT_MULTICAST = 1u,  // 2-CTA tiles: one multicast commit instead of two plain commits
   // Tiles start their K range at different K blocks and wrap around.  Set by the plan for skinny
   // (weight-streaming) problems: all CTAs walking K in step read addresses that differ only by
   // multiples of the row pitch, which loads the HBM channels unevenly (measured: 24.5 -> 23.4 us at
@@ -204,7 +203,7 @@ __device__ __forceinline__ bool aborted(const Abort& ab) {
   return *reinterpret_cast<volatile uint32_t*>(ab.flag) != 0;
 }
 
-__device__ __noinline__ void record_timeout(const Abort& ab, uint32_t code, uint32_t tile,
+static __device__ __noinline__ void record_timeout(const Abort& ab, uint32_t code, uint32_t tile,
                                             uint32_t kb) {
   if (atomicCAS(ab.status, 0u, code) == 0u) {
     ab.status[1] = blockIdx.x;
@@ -714,8 +713,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const int32_t row0 = is_b ? static_cast<int32_t>(tn * BN + work.col_off + rank * (work.cols / CTAS))
                                 : static_cast<int32_t>(tm * (Cfg::BM * CTAS) + rank * Cfg::BM);
       const uint32_t nkb = kb_hi - kb_lo;
-      const uint32_t stagger_mul = ((p.tune >> 8) & 0xFFu) ? ((p.tune >> 8) & 0xFFu) : 31u;  // bits 8..15: override
-      const uint32_t rot = (p.tune & TUNE_K_STAGGER) ? (t * stagger_mul) % nkb : 0u;
+      const uint32_t rot = (p.tune & TUNE_K_STAGGER) ? (t * 31u) % nkb : 0u;
       for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
         const long long w0 = PROF ? clock64() : 0;
         const bool got = detail::wait(empty_bar(stage), phase ^ 1u, ab, WAIT_PRODUCER_EMPTY, t, kb);
@@ -784,7 +782,6 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       long long prof_full = 0, prof_tmem = 0, prof_tmem1 = 0, prof_issue = 0;
       const long long prof_t0 = PROF ? clock64() : 0;
       const uint64_t prof_ns0 = PROF ? ptx::globaltimer_ns() : 0;
-      const bool mcast = (p.tune & TUNE_COMMIT_MULTICAST) != 0u;
       const uint32_t a_hi = p.a.desc_hi, b_hi = p.b.desc_hi;
       const uint32_t a_lo0 = ((base >> 4) & 0x3FFFu) | p.a.desc_lo;
       const uint32_t b_lo0 = (((base + Cfg::A_BYTES) >> 4) & 0x3FFFu) | p.b.desc_lo;
@@ -815,16 +812,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         };
         // Release stage `st` to the producer(s) once the MMAs issued so far have read it.
         auto release_stage = [&](uint32_t st) {
-          if constexpr (CTAS == 2) {
-            if (mcast) {
-              ptx::tc_commit_pair(empty_bar(st));
-            } else {
-              ptx::tc_commit<CTAS>(empty_bar(st));
-              ptx::tc_commit<CTAS>(ptx::mapa(empty_bar(st), 1));
-            }
-          } else {
-            ptx::tc_commit<CTAS>(empty_bar(st));
-          }
+          ptx::tc_commit<CTAS>(empty_bar(st));
+          if constexpr (CTAS == 2) ptx::tc_commit<CTAS>(ptx::mapa(empty_bar(st), 1));
         };
         uint32_t kb = kb_lo;
         if constexpr (Cfg::MB == 2) {
@@ -903,16 +892,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
           for (uint32_t mb = 0; mb < static_cast<uint32_t>(Cfg::MB); ++mb) {
             const uint32_t fb = tmem_full_bar(acc + mb);
-            if constexpr (CTAS == 2) {
-              if (mcast) {
-                ptx::tc_commit_pair(fb);
-              } else {
-                ptx::tc_commit<CTAS>(fb);
-                ptx::tc_commit<CTAS>(ptx::mapa(fb, 1));
-              }
-            } else {
-              ptx::tc_commit<CTAS>(fb);
-            }
+            ptx::tc_commit<CTAS>(fb);
+            if constexpr (CTAS == 2) ptx::tc_commit<CTAS>(ptx::mapa(fb, 1));
           }
         }
         __syncwarp();

@@ -101,7 +101,9 @@ struct sm100_gemm {
   // One asynchronous launch on `stream`; D may alias C; C is not read when beta == 0.
   void operator()(const TIn* a, const TIn* b, const TOut* c, TOut* d, const TOut alpha,
                   const TOut beta, cudaStream_t stream) {
-    if constexpr (std::is_same_v<TIn, std::int8_t>) {
+    // The C ABI reads int32 scalars exactly when the OUTPUT type is s32; an s8 GEMM with a
+    // floating-point output (dequantising) takes float scalars like every other float output.
+    if constexpr (std::is_same_v<TOut, std::int32_t>) {
       const std::int32_t al = static_cast<std::int32_t>(alpha), be = static_cast<std::int32_t>(beta);
       checkGzStatus(gz_gemm_run(plan_, a, b, c, d, &al, &be, stream), "sm100_gemm::operator()");
     } else {

@@ -165,8 +165,10 @@ GZ_API gz_status gz_gemm_plan_info(const gz_plan* plan, gz_plan_info* info);
 /* Diagnostics: give the plan a device buffer of 16 * info.grid 64-bit words and
  * every later launch records, per CTA, the clocks its producer, MMA and epilogue
  * roles spent waiting (layout: see GemmParams::prof in csrc/sm100_gemm.cuh).
- * NULL switches it off again.  Counters are compiled in for bf16 -> bf16 plans only;
- * others return GZ_ERR_UNSUPPORTED.  No counterpart in the reference. */
+ * NULL switches it off again.  The buffer must hold at least 16 * info.grid words: nothing checks
+ * a raw pointer's size.  Counters are compiled in for bf16 -> bf16 plans of one tile shape per
+ * family (GZ_CFG_1CTA_N64, GZ_CFG_2CTA_N256, GZ_CFG_2CTA_M512_N256, GZ_CFG_SWAP_M16); other plans
+ * return GZ_ERR_UNSUPPORTED.  No counterpart in the reference. */
 GZ_API gz_status gz_gemm_plan_set_profile(gz_plan* plan, void* device_words);
 
 /* Asynchronous on `stream` (a cudaStream_t passed as void*; NULL = legacy default stream).
@@ -212,6 +214,18 @@ GZ_API gz_status gz_gemm_run_ex(gz_plan* plan, const void* a, const void* b, con
 GZ_API gz_status gz_gemm_run_host(gz_plan* plan, const void* a, const void* b, const void* c, void* d,
                                   const void* alpha, const void* beta, void* stream);
 
+/* gz_gemm_run_host for one GPU of a column-partitioned run (one plan per GPU, each for its own
+ * column block; the reference harness is single-GPU, nvidia/utils/benchmark.cuh:20, so this has no
+ * counterpart there).  With GZ_HOST_A_ON_DEVICE, `a` is a DEVICE pointer on the plan's GPU whose
+ * contents are valid in the order of `stream`: the replicated operand, of which every GPU uploaded
+ * only a slice and which was then gathered GPU to GPU, instead of crossing the host's PCIe fabric
+ * once per GPU.  b, c, d stay host pointers.  The uploads of B start at once on the plan's copy
+ * stream (they do not wait for work already queued on `stream`, such as that gather); the GEMMs
+ * run on `stream`, after it.  host_flags == 0 is gz_gemm_run_host. */
+#define GZ_HOST_A_ON_DEVICE 0x1u
+GZ_API gz_status gz_gemm_run_host_ex(gz_plan* plan, const void* a, const void* b, const void* c, void* d,
+                                     const void* alpha, const void* beta, void* stream, uint32_t host_flags);
+
 /* The same skinny (M <= 128) split-K GEMM for hosts that must not allocate.  This entry point has
  * no counterpart in the reference.  It exists for callers that gave all device memory to their own
  * allocator at start-up and may not call cudaMalloc afterwards (it could fail against their budget
@@ -227,12 +241,25 @@ GZ_API gz_status gz_gemm_run_host(gz_plan* plan, const void* a, const void* b, c
  *   - The first call on a device looks up the array's device address and opts the kernel into its
  *     shared-memory size; make that first call before any stream capture.
  *   - Every call on a device shares the one array.  It keeps the previous call's contents; what
- *     must start at zero is cleared on `stream` before the launch.  Two calls that overlap on the
- *     GPU (different streams, or different threads) race on it: serialise them.
+ *     must start at zero (the arrival counters) is cleared on `stream` before the launch.  Two
+ *     calls that overlap on the GPU (different streams, or different threads) race on it:
+ *     serialise them.
+ *   - A bounded wait that expires inside the kernel is reported by gz_static_last_device_status,
+ *     not by this call (which only launches).
  * Asynchronous on `stream`. */
 #define GZ_STATIC_SCRATCH_BYTES (8u << 20)
 GZ_API gz_status gz_gemm_skinny_static(const gz_gemm_desc* desc, const void* a, const void* b, const void* c,
                                        void* d, const void* alpha, const void* beta, void* stream);
+
+/* Failure detection for gz_gemm_skinny_static, which has no plan to ask (no counterpart in the
+ * reference; allocates nothing either).  The kernel's four status words live at the end of the
+ * same fixed array.  They keep the FIRST bounded wait that expired in any gz_gemm_skinny_static
+ * launch on `device` until this call reads them: it blocks until `stream` is idle, copies the 16
+ * bytes, clears them if set, and returns GZ_ERR_DEVICE_TIMEOUT (detail as for
+ * gz_last_device_status; may be NULL) or GZ_OK.  After a timeout D is partly written; the array
+ * and the context stay usable, and the next gz_gemm_skinny_static call clears what the aborted
+ * launch left in the arrival counters. */
+GZ_API gz_status gz_static_last_device_status(int32_t device, void* stream, uint32_t detail[4]);
 
 /* Synchronises the plan's device status word: returns GZ_OK, or
  * GZ_ERR_DEVICE_TIMEOUT if a bounded wait expired in any launch since the last

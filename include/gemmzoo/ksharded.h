@@ -3,9 +3,9 @@
  *   D[:, J_r] = alpha * sum_g A[:, K_g] * B[K_g, J_r] + beta * C[:, J_r]      on rank r
  *
  * Rank g holds the K slice (A[:, K_g], B[K_g, :]) and ends up with the column block J_r of D
- * (N / world columns).  No counterpart exists in the reference (it is single-GPU); this is the
- * optional multi-GPU item of the build's north star: "K sliced across GPUs, fp32 partials,
- * reduce-scatter over N".  Instead of computing a full partial and then calling a collective, the
+ * (N / world columns).  No counterpart exists in the reference (it is single-GPU): this serves
+ * weights that are already sharded along K, whose fp32 partial products must be reduce-scattered
+ * over N.  Instead of computing a full partial and then calling a collective, the
  * GEMM's epilogue stores every column block of its fp32 (int32 for s8) partial sums straight into
  * the memory of the GPU that owns the block (plain peer stores over NVLink, tile by tile while the
  * main loop runs); a one-warp kernel then raises a flag on every peer, and the owner's reduce kernel

@@ -1,11 +1,11 @@
-"""The five configurations of BASELINE.json on the GPU, at full size.
+"""The five benchmark configurations of the build specification on the GPU, at full size.
 
-Full CPU comparison up to 4096^3; above that all columns of 64 seeded rows are
-compared (the same kernel computes every row the same way, and the properties in
-test_properties.py tie the rest together).  Operands are generated on the device
+Full CPU comparison up to 4096^3; above that all columns of 64 seeded rows and all
+rows of 64 seeded columns are compared (the properties in test_properties.py tie the
+rest together).  Operands are generated on the device
 with gz_fill (seeded, distinct streams per operand) and copied back for the oracle.
 
-Tolerances: s8 bit-exact; bf16/fp16 max |D-R| / max |R| <= 1e-2 (BASELINE.json) and
+Tolerances: s8 bit-exact; bf16/fp16 max |D-R| / max |R| <= 1e-2 (the specification's bar) and
 the per-element bars of tests/helpers.py; tf32 |D-R| <= 2^-9 * sum|a||b|."""
 import numpy as np
 import pytest
@@ -36,8 +36,13 @@ def run_config(in_t, out_t, tin, tout, m, n, k, b_col, seed, dist_a, scale_a, di
     ah, bh = orc.bits_of(a), orc.bits_of(b)
     ch = orc.bits_of(c) if c is not None else None
     dh = d.cpu()
+    cols = None
     if rows is not None:
+        # Above 4096^3: all columns of `rows` seeded rows AND all rows of as many seeded columns.
+        cols = np.sort(np.random.default_rng(seed + 1000).choice(n, size=min(rows, n), replace=False))
         rows = np.sort(np.random.default_rng(seed).choice(m, size=min(rows, m), replace=False))
+        check_columns(in_t, out_t, ah, bh, ch, c.double().cpu().numpy() if c is not None else None, dh, m, n, k, b_col,
+                      alpha, beta, cols)
     got = dh if rows is None else dh[torch.from_numpy(rows)]
     if in_t == gz.DT_S8:
         ref = orc.gemm_s8(ah, bh, ch, m, n, k, alpha=int(alpha), beta=int(beta), b_col_major=b_col, rows=rows)
@@ -58,6 +63,30 @@ def run_config(in_t, out_t, tin, tout, m, n, k, b_col, seed, dist_a, scale_a, di
         unit = 2.0 ** -8 if out_t == gz.DT_BF16 else 2.0 ** -10
         assert (err <= unit * np.abs(ref) + 2.0 ** -20 * scale + 1e-7).all()
     return g.info()
+
+
+def check_columns(in_t, out_t, ah, bh, ch, c_f64, dh, m, n, k, b_col, alpha, beta, cols):
+    """Every row of the output columns `cols` against the oracle: the oracle runs on the
+    m x len(cols) problem whose B holds just those columns (a fault confined to one row block of
+    one tile column, which 64 sampled rows could miss, shows up here)."""
+    bsub = np.ascontiguousarray(bh[cols] if b_col else bh[:, cols])
+    csub = np.ascontiguousarray(ch[:, cols]) if ch is not None else None
+    nc = len(cols)
+    got = dh[:, torch.from_numpy(cols)]
+    if in_t == gz.DT_S8:
+        ref = orc.gemm_s8(ah, bsub, csub, m, nc, k, alpha=int(alpha), beta=int(beta), b_col_major=b_col)
+        assert np.array_equal(got.numpy(), ref)
+        return
+    ref = orc.gemm_f64(in_t, out_t, ah, bsub, csub, m, nc, k, alpha=alpha, beta=beta, b_col_major=b_col)
+    scale = orc.abs_gemm(in_t, ah, bsub, m, nc, k, b_col_major=b_col) * abs(alpha)
+    if c_f64 is not None:
+        scale += abs(beta) * np.abs(c_f64[:, cols])
+    err = np.abs(got.double().numpy() - ref)
+    if in_t == gz.DT_F32:
+        assert (err <= 2.0 ** -9 * scale + 1e-30).all(), (err / scale).max()
+    else:
+        unit = 2.0 ** -8 if out_t == gz.DT_BF16 else 2.0 ** -10
+        assert (err <= unit * np.abs(ref) + 2.0 ** -20 * scale + 1e-7).all()
 
 
 def test_config1_fp16_1024():

@@ -43,3 +43,32 @@ def test_host_operands_match_device_operands(in_t, out_t, tin, tout, m, n, k, b_
         else:
             assert torch.equal(got, want.cpu())
     assert g.plan.device_status()[0] == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(300, 520, 256), (1024, 8192 + 300, 1024)])
+def test_resident_a_host_b_matches_device_operands(m, n, k):
+    """gz_gemm_run_host_ex with GZ_HOST_A_ON_DEVICE: A already sits in the GPU's memory (the
+    replicated operand of a column-partitioned run), B, C and D are host memory; the result equals
+    the device-operand run bit for bit, also when A only becomes valid through work queued on the
+    caller's stream just before the call (the uploads of B do not wait for it, the GEMMs do)."""
+    gen = torch.Generator().manual_seed(m)
+    a = torch.randn(m, k, generator=gen).bfloat16().pin_memory()
+    b = (torch.randn(n, k, generator=gen) * k ** -0.5).bfloat16().pin_memory()
+    c = torch.randn(m, n, generator=gen).bfloat16().pin_memory()
+    g = gz.Sm100Gemm(m, n, k, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR)
+    want = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    g(a.to(DEV), b.to(DEV), c.to(DEV), want, 1.5, 1.0)
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream()
+    a_dev = torch.zeros(m, k, dtype=torch.bfloat16, device=DEV)
+    for call in range(2):
+        a_dev.zero_()
+        a_dev.copy_(a, non_blocking=True)  # queued on the caller's stream, not yet done when the call starts
+        got = torch.full((m, n), 3, dtype=torch.bfloat16).pin_memory()
+        g.plan.run_host(a_dev, b, c, got, 1.5, 1.0, stream, a_on_device=True)
+        assert torch.equal(got.view(torch.int16), want.cpu().view(torch.int16)), call
+    # the same plan still takes a host A afterwards
+    got = torch.full((m, n), 3, dtype=torch.bfloat16).pin_memory()
+    g.plan.run_host(a, b, c, got, 1.5, 1.0, stream)
+    assert torch.equal(got.view(torch.int16), want.cpu().view(torch.int16))
+    assert g.plan.device_status()[0] == 0

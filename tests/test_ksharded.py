@@ -45,7 +45,7 @@ def _expected(a, b_nk, c_full, alpha, beta, out_t):
     (gz.DT_F16, gz.DT_F16, 384, 1024, 768, 2, 1, 0),        # 128x128 / 256x256 tiles, direct stores
     (gz.DT_F32, gz.DT_F32, 256, 512, 512, 4, 1, 0),         # tf32
     (gz.DT_S8, gz.DT_S32, 300, 768, 2048, 3, 3, -2),        # int32 partial sums, world not a power of two
-    (gz.DT_BF16, gz.DT_BF16, 1, 14336, 4096, 8, 1, 0),      # the north star's skinny shape over 8 ranks
+    (gz.DT_BF16, gz.DT_BF16, 1, 14336, 4096, 8, 1, 0),      # the inference-shaped skinny problem over 8 ranks
 ])
 def test_emulated_ranks_match_unsharded(in_t, out_t, m, n, k, world, alpha, beta):
     lo, hi = (-128, 128) if in_t == gz.DT_S8 else (-3, 4)

@@ -1,4 +1,4 @@
-"""Size-independent properties checked on the GPU, some at BASELINE.json's largest
+"""Size-independent properties checked on the GPU, some at the largest benchmark
 size (bf16 16384^3): multiplying by the identity returns A bit for bit, a
 column-partitioned run equals the unpartitioned one bit for bit, repeated runs are
 bitwise identical, and integer GEMM is linear."""
