@@ -18,6 +18,7 @@ CFG_2CTA_M512_N256 = 10
 FLAG_EPILOGUE_DIRECT, FLAG_EPILOGUE_TMA, FLAG_TEST_WITHHOLD_ACC_READY = 0x1, 0x2, 0x80000000
 FLAG_NO_SPLIT_K, FLAG_SPLIT_K = 0x4, 0x8
 FLAG_BROADCAST_A, FLAG_BROADCAST_B = 0x10, 0x20
+FLAG_NO_DIE_ORDER = 0x40
 HOST_A_ON_DEVICE = 0x1
 
 GZ_OK = 0
@@ -31,6 +32,7 @@ EXPORTED_SYMBOLS = [
     "gz_gemm_run", "gz_gemm_run_ex", "gz_gemm_run_host", "gz_gemm_run_host_ex", "gz_gemm_skinny_static", "gz_static_last_device_status",
     "gz_last_device_status", "gz_status_string",
     "gz_last_cuda_error", "gz_fill", "gz_tile_coords", "gz_partition_columns", "gz_version",
+    "gz_device_placement", "gz_classify_dies",
 ]
 
 
@@ -87,6 +89,7 @@ class PlanInfo(C.Structure):
         ("split_k", C.c_int32), ("reserved", C.c_int32),
         ("tiles", C.c_int64), ("workspace_bytes", C.c_int64),
         ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64), ("ldd", C.c_int64),
+        ("die_order", C.c_int32), ("reserved2", C.c_int32),
     ]
 
     def as_dict(self):
@@ -154,6 +157,10 @@ def lib():
     L.gz_tile_coords.restype = None
     L.gz_partition_columns.argtypes = [i64, i32, i32, i64, C.POINTER(i64), C.POINTER(i64)]
     L.gz_partition_columns.restype = C.c_int
+    L.gz_device_placement.argtypes = [i32, vp, C.POINTER(i32 * 2)]
+    L.gz_device_placement.restype = C.c_int
+    L.gz_classify_dies.argtypes = [vp, i32, i32, vp, C.POINTER(i32 * 2)]
+    L.gz_classify_dies.restype = C.c_int
     L.gz_version.argtypes = []
     L.gz_version.restype = i32
     _lib = L
@@ -183,6 +190,25 @@ def partition_columns(n, parts, p, align=8):
     if st != GZ_OK:
         raise GzError(st, "gz_partition_columns")
     return b.value, e.value
+
+
+def classify_dies(clocks):
+    """gz_classify_dies on a (sms x lines) uint32 numpy array.  Returns (status, die_of_sm list, [n0, n1])."""
+    import numpy as np
+    c = np.ascontiguousarray(clocks, dtype=np.uint32)
+    sms, lines = c.shape
+    dies = (C.c_uint8 * 160)()
+    counts = (C.c_int32 * 2)()
+    st = lib().gz_classify_dies(c.ctypes.data, sms, lines, C.addressof(dies), C.byref(counts))
+    return st, list(dies)[:sms], list(counts)
+
+
+def device_placement(device=0):
+    """gz_device_placement: (status, die_of_sm list, [n0, n1])."""
+    dies = (C.c_uint8 * 160)()
+    counts = (C.c_int32 * 2)()
+    st = lib().gz_device_placement(device, C.addressof(dies), C.byref(counts))
+    return st, list(dies), list(counts)
 
 
 def _scalar(in_type, v, out_type=None):

@@ -16,12 +16,15 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <new>
 #include <string>
+#include <vector>
 
 #include "gemmzoo/gemm.h"
 #include "kernel_table.h"
+#include "placement.cuh"
 #include "rng.h"
 #include "simt_gemm.cuh"
 #include "sm100_gemm.cuh"
@@ -147,7 +150,7 @@ gz_status normalise(const gz_gemm_desc* desc, Problem* pr) {
     return GZ_ERR_INVALID_ARG;
   if ((d.flags & GZ_FLAG_NO_SPLIT_K) && (d.flags & GZ_FLAG_SPLIT_K)) return GZ_ERR_INVALID_ARG;
   if (d.flags & ~(GZ_FLAG_EPILOGUE_DIRECT | GZ_FLAG_EPILOGUE_TMA | GZ_FLAG_NO_SPLIT_K | GZ_FLAG_SPLIT_K |
-                  GZ_FLAG_BROADCAST_A | GZ_FLAG_BROADCAST_B | GZ_FLAG_TEST_WITHHOLD_ACC_READY))
+                  GZ_FLAG_BROADCAST_A | GZ_FLAG_BROADCAST_B | GZ_FLAG_NO_DIE_ORDER | GZ_FLAG_TEST_WITHHOLD_ACC_READY))
     return GZ_ERR_INVALID_ARG;
   if (d.batch == 0) d.batch = 1;
   if (d.batch < 0 || d.batch > 65535 || d.stride_a < 0 || d.stride_b < 0 || d.stride_c < 0 || d.stride_d < 0)
@@ -165,12 +168,26 @@ gz_status normalise(const gz_gemm_desc* desc, Problem* pr) {
   // Tile coordinates and TMA coordinates are 32-bit.
   const int64_t lim = (int64_t(1) << 31) - 1024;
   if (d.m > lim || d.n > lim || d.k > lim) return GZ_ERR_TOO_LARGE;
-  if (cdiv(d.m, 128) * cdiv(d.n, 64) * d.batch > (int64_t(1) << 31) - 1) return GZ_ERR_TOO_LARGE;
+  // at most 2^49 tiles of the smallest shape per problem, so the product with the batch (< 2^16)
+  // is taken in two steps
+  const int64_t tiles_min = cdiv(d.m, 128) * cdiv(d.n, 64);
+  if (tiles_min > (int64_t(1) << 31) - 1 || tiles_min * d.batch > (int64_t(1) << 31) - 1) return GZ_ERR_TOO_LARGE;
+  // A matrix must be addressable: rows x leading dimension (and that times the batch) within 2^60 elements.
+  const int64_t addr_lim = int64_t(1) << 60;
+  auto span = [&](int64_t rows, int64_t ld, int64_t* out) {
+    return !__builtin_mul_overflow(rows, ld, out) && *out <= addr_lim / d.batch;
+  };
+  int64_t span_a, span_b, span_c, span_d;
+  if (!span(d.layout_a == GZ_ROW_MAJOR ? d.m : d.k, d.lda, &span_a) ||
+      !span(d.layout_b == GZ_ROW_MAJOR ? d.k : d.n, d.ldb, &span_b) || !span(d.m, d.ldc, &span_c) ||
+      !span(d.m, d.ldd, &span_d) || d.stride_a > addr_lim / d.batch || d.stride_b > addr_lim / d.batch ||
+      d.stride_c > addr_lim / d.batch || d.stride_d > addr_lim / d.batch)
+    return GZ_ERR_TOO_LARGE;
   // Batch strides: packed by default; a broadcast operand has none.
-  if (d.stride_a == 0) d.stride_a = (d.layout_a == GZ_ROW_MAJOR ? d.m : d.k) * d.lda;
-  if (d.stride_b == 0) d.stride_b = (d.layout_b == GZ_ROW_MAJOR ? d.k : d.n) * d.ldb;
-  if (d.stride_c == 0) d.stride_c = d.m * d.ldc;
-  if (d.stride_d == 0) d.stride_d = d.m * d.ldd;
+  if (d.stride_a == 0) d.stride_a = span_a;
+  if (d.stride_b == 0) d.stride_b = span_b;
+  if (d.stride_c == 0) d.stride_c = span_c;
+  if (d.stride_d == 0) d.stride_d = span_d;
   if (d.flags & GZ_FLAG_BROADCAST_A) d.stride_a = 0;
   if (d.flags & GZ_FLAG_BROADCAST_B) d.stride_b = 0;
   if (d.wait_limit_ns == 0) d.wait_limit_ns = 2000000000ull;
@@ -448,13 +465,58 @@ bool encode_2d(CUtensorMap* tm, int dt, const void* base, uint64_t dim0, uint64_
   return true;
 }
 
+// Placement of each device, measured at most once per process (see placement.cuh).
+gz::DevicePlacement g_placement[64];
+bool g_placement_done[64] = {};
+std::mutex g_placement_mu;
+
+const gz::DevicePlacement* placement_of(int device, int sm_count) {
+  if (device < 0 || device >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_placement_mu);
+  if (!g_placement_done[device]) {
+    g_placement[device] = gz::measure_placement(sm_count);  // the device is current (plan creation)
+    g_placement_done[device] = true;
+  }
+  return &g_placement[device];
+}
+
+// The die-aware order pays where a launch fills the whole machine for several waves of tiles: then
+// what the two dies read in a wave is large against the L2, and keeping their tiles apart saves
+// die-to-die traffic.  Skinny (swapped) problems stream their weight matrix once and gain nothing.
+bool wants_die_order(const Problem& pr, const CfgShape& s, int sm_count, int64_t all_tiles) {
+  if (s.swap || (pr.d.flags & GZ_FLAG_NO_DIE_ORDER)) return false;
+  const int64_t units = sm_count / s.ctas;
+  return units * s.ctas == sm_count && all_tiles >= 3 * units;
+}
+
 }  // namespace
+
+// Encoded tensor maps of one set of operand pointers.  A tensor map embeds the base address, and
+// callers such as the reference's harness rotate their operand buffers every call
+// (nvidia/utils/benchmark.cuh:80-83), so a plan keeps the last few sets instead of encoding three
+// maps per launch.  Extents, strides and boxes are constants of the plan.
+struct TensorMapSet {
+  const void* a = nullptr;
+  const void* b = nullptr;
+  const void* d = nullptr;  // null when the launch does not store through TMA
+  uint64_t stamp = 0;       // 0 = empty; otherwise the plan's clock at the last use
+  CUtensorMap ta, tb, td;
+};
 
 struct gz_plan {
   Problem pr;
   gz_plan_info info;
   KernelEntry entry;
   gz::GemmParams base;  // everything that does not depend on the operand pointers
+  // Die-aware tile order: ticket counters, one set of four words per launch in flight (see
+  // GemmParams::die_tickets); launches take the sets in turn.
+  static constexpr int kDieTicketSets = 32;
+  uint32_t* die_tickets = nullptr;
+  std::atomic<uint32_t> launch_seq{0};
+  static constexpr int kTensorMapSets = 8;
+  TensorMapSet tmaps[kTensorMapSets];
+  uint64_t tmap_clock = 0;
+  std::mutex tmap_mu;
   uint32_t* status_dev;
   void* workspace;  // split-K partial sums followed by the per-tile arrival counters
   // device staging for gz_gemm_run_host
@@ -709,6 +771,21 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** out, const gz_gemm_desc* desc) {
     p.ldd = pr.d.ldd;
     p.status = pl->status_dev;
     p.wait_limit_ns = pr.d.wait_limit_ns;
+    if (wants_die_order(pr, s, sm_count, all_tiles)) {
+      const gz::DevicePlacement* place = placement_of(pr.d.device, sm_count);
+      if (place && place->known) {
+        const size_t bytes = gz_plan::kDieTicketSets * 4 * sizeof(uint32_t);
+        if (!cuda_ok(cudaMalloc(&pl->die_tickets, bytes), "cudaMalloc(die tickets)") ||
+            !cuda_ok(cudaMemset(pl->die_tickets, 0, bytes), "cudaMemset(die tickets)")) {
+          if (pl->die_tickets) cudaFree(pl->die_tickets);
+          cudaFree(pl->status_dev);
+          delete pl;
+          return GZ_ERR_OUT_OF_MEMORY;
+        }
+        std::memcpy(p.die_of_sm, place->die_of_sm, sizeof(p.die_of_sm));
+        pl->info.die_order = 1;
+      }
+    }
     if (pl->info.split_k) {
       const size_t ws_bytes = (size_t)pl->info.workspace_bytes;
       const size_t counter_bytes = (size_t)all_tiles * 4;
@@ -734,6 +811,7 @@ GZ_API gz_status gz_gemm_plan_destroy(gz_plan* pl) {
   if (!pl) return GZ_ERR_INVALID_ARG;
   DeviceGuard guard(pl->pr.d.device);
   if (pl->status_dev) cudaFree(pl->status_dev);
+  if (pl->die_tickets) cudaFree(pl->die_tickets);
   if (pl->workspace) cudaFree(pl->workspace);
   if (pl->ha) cudaFree(pl->ha);
   if (pl->hb) cudaFree(pl->hb);
@@ -762,6 +840,40 @@ GZ_API gz_status gz_gemm_plan_set_profile(gz_plan* pl, void* device_words) {
       return GZ_ERR_CUDA;
   }
   pl->base.prof = static_cast<unsigned long long*>(device_words);
+  return GZ_OK;
+}
+
+GZ_API gz_status gz_classify_dies(const uint32_t* clocks, int32_t sms, int32_t lines, uint8_t* die_of_sm,
+                                  int32_t sms_on_die[2]) {
+  if (!clocks || !die_of_sm || !sms_on_die || sms <= 0 || sms > 160 || lines <= 0) return GZ_ERR_INVALID_ARG;
+  std::vector<uint32_t> v(clocks, clocks + static_cast<size_t>(sms) * lines);
+  int counts[2] = {0, 0};
+  uint8_t dies[160] = {};
+  const bool ok = gz::classify_dies(v, sms, lines, dies, counts);
+  if (!ok) return GZ_ERR_UNSUPPORTED;
+  std::memcpy(die_of_sm, dies, static_cast<size_t>(sms));
+  sms_on_die[0] = counts[0];
+  sms_on_die[1] = counts[1];
+  return GZ_OK;
+}
+
+GZ_API gz_status gz_device_placement(int32_t device, uint8_t* die_of_sm, int32_t sms_on_die[2]) {
+  if (!die_of_sm || !sms_on_die) return GZ_ERR_INVALID_ARG;
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+    (void)cudaGetLastError();
+    return GZ_ERR_NO_DEVICE;
+  }
+  if (device < 0 || device >= ndev || device >= 64) return GZ_ERR_INVALID_ARG;
+  int sms = 0;
+  if (!cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "device attribute")) return GZ_ERR_CUDA;
+  DeviceGuard guard(device);
+  if (!guard.ok()) return GZ_ERR_CUDA;
+  const gz::DevicePlacement* place = placement_of(device, sms);
+  if (!place || !place->known) return GZ_ERR_UNSUPPORTED;
+  std::memcpy(die_of_sm, place->die_of_sm, static_cast<size_t>(sms));
+  sms_on_die[0] = place->sms_on_die[0];
+  sms_on_die[1] = place->sms_on_die[1];
   return GZ_OK;
 }
 
@@ -886,7 +998,29 @@ gz_status run_impl(gz_plan* pl, const void* a, const void* b, const void* c, voi
     p.d_vec_ok = vec ? 1u : 0u;
   }
 
+  if (pl->die_tickets)
+    p.die_tickets = pl->die_tickets + 4u * (pl->launch_seq.fetch_add(1u, std::memory_order_relaxed) % gz_plan::kDieTicketSets);
   CUtensorMap ta, tb, td;
+  const void* const d_key = p.epilogue_tma ? d : nullptr;
+  bool cached = false;
+  {
+    std::lock_guard<std::mutex> lock(pl->tmap_mu);
+    for (TensorMapSet& e : pl->tmaps) {
+      if (e.stamp != 0 && e.a == a && e.b == b && e.d == d_key) {
+        ta = e.ta;
+        tb = e.tb;
+        td = e.td;
+        e.stamp = ++pl->tmap_clock;
+        cached = true;
+        break;
+      }
+    }
+  }
+  const LaunchFn fn = p.prof ? pl->entry.launch_prof : pl->entry.launch;
+  if (cached) {
+    if (!cuda_ok(fn(ta, tb, td, p, pl->info.grid, stream), "kernel launch")) return GZ_ERR_CUDA;
+    return GZ_OK;
+  }
   const uint32_t bk = 128u / pr.in_size;
   // Tensor map of one input matrix: `rows` is its M (or N) extent, `od` the kernel operand it feeds.
   auto encode_input = [&](CUtensorMap* tm, const void* base, bool mn_major, int64_t rows, int64_t ld,
@@ -915,7 +1049,19 @@ gz_status run_impl(gz_plan* pl, const void* a, const void* b, const void* c, voi
   } else {
     td = ta;  // unused by the kernel in this mode
   }
-  const LaunchFn fn = p.prof ? pl->entry.launch_prof : pl->entry.launch;
+  {
+    std::lock_guard<std::mutex> lock(pl->tmap_mu);
+    TensorMapSet* victim = &pl->tmaps[0];
+    for (TensorMapSet& e : pl->tmaps)
+      if (e.stamp < victim->stamp) victim = &e;  // an empty slot, else the least recently used
+    victim->a = a;
+    victim->b = b;
+    victim->d = d_key;
+    victim->ta = ta;
+    victim->tb = tb;
+    victim->td = td;
+    victim->stamp = ++pl->tmap_clock;
+  }
   if (!cuda_ok(fn(ta, tb, td, p, pl->info.grid, stream), "kernel launch"))
     return GZ_ERR_CUDA;
   return GZ_OK;

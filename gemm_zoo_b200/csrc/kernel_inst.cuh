@@ -26,15 +26,23 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
   cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  unsigned na = 0;
+  // Programmatic dependent launch: this grid may be scheduled while the previous kernel of the
+  // stream is still running; it sets itself up (barriers, tensor memory, descriptor prefetch) and
+  // then waits in the kernel (griddepcontrol.wait) before it touches global memory.
+  attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[na].val.programmaticStreamSerializationAllowed = 1;
+  ++na;
   if (Cfg::CTAS > 1) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = Cfg::CTAS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = Cfg::CTAS;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
   }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
   return cudaLaunchKernelEx(&cfg, sm100_gemm_kernel<Cfg, PROF>, ta, tb, td, p);
 }
 

@@ -33,6 +33,13 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Index of the SM this thread runs on.
+__device__ __forceinline__ uint32_t smid() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
+  return r;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -82,6 +89,17 @@ __device__ __forceinline__ void named_barrier_arrive(uint32_t id, uint32_t threa
 
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
+// Programmatic dependent launch.  launch_dependents: the next kernel of the stream (if it was
+// launched with programmatic serialization) may be scheduled once every CTA of this grid has said so
+// or exited.  wait: blocks until the kernels this grid depends on have completed and their memory
+// operations are visible; a no-op for a grid launched the ordinary way.
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- mbarrier

@@ -121,7 +121,8 @@ struct GemmParams {
   // Optional epilogue terms (floating-point outputs only), applied in fp32:
   //   D = act(alpha * row_scale[i] * col_scale[j] * acc + beta * C + bias[j])
   // epi_flags != 0 says that at least one of them is present (bit 0 bias, 1 row_scale,
-  // 2 col_scale, 3 activation); the kernel then takes its slice-by-slice epilogue.
+  // 2 col_scale, 3 activation); the kernel then takes its slice-by-slice epilogue (the terms,
+  // above all the activations, are too much code to unroll over a warp's whole share).
   uint32_t epi_flags;
   uint32_t act;  // 0 none, 1 relu, 2 gelu (erf), 3 gelu (tanh), 4 silu
   const float* bias;
@@ -129,6 +130,17 @@ struct GemmParams {
   const float* col_scale;
   // Scheduling switches set by the plan (see TUNE_* below).
   uint32_t tune;
+  // Die-aware tile order (die_tickets == null: off).  A B200 is two dies, each with its own half
+  // of the L2; a line that the SMs of both dies read crosses the die-to-die link.  With the order
+  // on, the CTA pairs of one die take neighbouring tiles of each wave: a pair looks up the die of
+  // its SM (die_of_sm, measured once per device by the plan), draws a ticket from that die's
+  // counter, and numbers itself from the bottom (die 0) or from the top (die 1) of [0, pairs).  Every
+  // pair draws exactly one ticket, so the numbers are a permutation wherever the hardware placed
+  // the CTAs: placement decides locality, never results.  The last pair to leave clears the
+  // counters.  die_tickets: 4 words (arrived on die 0, arrived on die 1, left, unused), zero
+  // between launches; two launches that overlap on the GPU must not share them.
+  uint32_t* die_tickets;
+  uint8_t die_of_sm[160];
   // Optional stall counters, 16 words per CTA (null = off):
   //  [0] A producer: clocks waiting for a free stage   [1] A producer: total clocks
   //  [2] MMA: clocks waiting for operand data          [3] MMA: clocks waiting for a free accumulator
@@ -187,7 +199,7 @@ struct GemmCfg {
   static_assert(MB == 1 || (MB == 2 && !SWAP), "one or two row blocks per CTA");
   static_assert(TMEM_COLS == 32 || TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
                 "TMEM allocation must be a power of two");
-  static_assert(8 * (2 * STAGES + 5) + 12 <= BAR_BYTES, "barrier area");
+  static_assert(8 * (2 * STAGES + 5) + 16 <= BAR_BYTES, "barrier area");
   static_assert(STAGE_BYTES % 1024 == 0, "stage must keep 1024-byte alignment");
 };
 
@@ -416,10 +428,22 @@ __device__ __forceinline__ void epilogue_math(uint32_t (&v)[32], const GemmParam
     float f[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) f[i] = alpha * acc_as_float<ACC_INT>(v[i]);
-    if (p.epi_flags != 0u && row_ok) {
+    // Optional terms.  The per-column vectors are fetched once per slice (lane l takes column
+    // col0 + l) and handed round by shuffles, which the whole warp executes.
+    const bool epi = p.epi_flags != 0u;
+    const uint32_t lane = ptx::lane_id();
+    const bool col_ok = lane < ncols;
+    if (epi) {
+      const float rs = (p.row_scale && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
+      const float my_cs = (p.col_scale && col_ok) ? __ldg(p.col_scale + col0 + lane) : 1.0f;
+      if (p.row_scale) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (static_cast<uint32_t>(i) < ncols) f[i] = epi_scale(p, f[i], row, col0 + i);
+        for (int i = 0; i < 32; ++i) f[i] *= rs;
+      }
+      if (p.col_scale) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) f[i] *= __shfl_sync(0xFFFFFFFFu, my_cs, i);
+      }
     }
     if (beta != 0.0f && row_ok) {
       if (ncols == 32 && p.c_vec_ok) {
@@ -439,10 +463,32 @@ __device__ __forceinline__ void epilogue_math(uint32_t (&v)[32], const GemmParam
           if (static_cast<uint32_t>(i) < ncols) f[i] = fmaf(beta, Tr::to_f(crow[i]), f[i]);
       }
     }
-    if (p.epi_flags != 0u && row_ok) {
+    if (epi) {
+      if (p.bias) {
+        const float my_bias = col_ok ? __ldg(p.bias + col0 + lane) : 0.0f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (static_cast<uint32_t>(i) < ncols) f[i] = epi_finish(p, f[i], col0 + i);
+        for (int i = 0; i < 32; ++i) f[i] += __shfl_sync(0xFFFFFFFFu, my_bias, i);
+      }
+      // one activation's code per pass over the slice, not five per element
+      switch (p.act) {
+        case 1:
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = activate(f[i], 1);
+          break;
+        case 2:
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = activate(f[i], 2);
+          break;
+        case 3:
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = activate(f[i], 3);
+          break;
+        case 4:
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = activate(f[i], 4);
+          break;
+        default: break;
+      }
     }
     if constexpr (sizeof(TOut) == 4) {
 #pragma unroll
@@ -624,11 +670,12 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars_ptr + 8 * (2 * STAGES + 5));
   uint32_t* const abort_flag = tmem_slot + 1;
   uint32_t* const split_flag = tmem_slot + 2;  // epilogue: "this CTA finishes the tile"
+  uint32_t* const order_slot = tmem_slot + 3;  // die-aware order: this CTA pair's number
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t rank = (CTAS == 2) ? ptx::cluster_ctarank() : 0u;
-  const uint32_t cluster = (CTAS == 2) ? ptx::cluster_id_x() : blockIdx.x;
+  const uint32_t hw_cluster = (CTAS == 2) ? ptx::cluster_id_x() : blockIdx.x;
   const uint32_t num_clusters = (CTAS == 2) ? ptx::num_clusters_x() : gridDim.x;
 
   const detail::Abort ab{abort_flag, p.status, p.wait_limit_ns};
@@ -679,8 +726,36 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   }
   if constexpr (CTAS == 2) ptx::cluster_wait_acquire();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  const long long setup_clocks = PROF ? clock64() - kernel_t0 : 0;
+
+  // Everything above touched only this CTA's shared and tensor memory and the kernel's parameters,
+  // so it may overlap the tail of the previous kernel of the stream; from here on global memory is
+  // read and written.  The next kernel may start its own set-up as soon as SMs come free.
+  ptx::grid_launch_dependents();
+  ptx::grid_dependency_wait();
   if constexpr (PROF) {
-    if (p.prof && threadIdx.x == 32) p.prof[16 * blockIdx.x + 14] = clock64() - kernel_t0;
+    if (p.prof && threadIdx.x == 32) p.prof[16 * blockIdx.x + 14] = setup_clocks;
+  }
+
+  // Which tiles this CTA (pair) takes: those of its hardware index, or, with the die-aware order,
+  // those of the number it draws now (see GemmParams::die_tickets).
+  uint32_t cluster = hw_cluster;
+  if (p.die_tickets != nullptr) {
+    if (rank == 0 && threadIdx.x == 0) {
+      const uint32_t die = p.die_of_sm[ptx::smid() % 160u] & 1u;
+      uint32_t r = atomicAdd(p.die_tickets + die, 1u);
+      if (r >= num_clusters) r = num_clusters - 1u;  // counters were not zero: another launch shares them
+      const uint32_t v = die == 0u ? r : num_clusters - 1u - r;
+      *reinterpret_cast<volatile uint32_t*>(order_slot) = v;
+      if constexpr (CTAS == 2) ptx::st_cluster_u32(ptx::mapa(ptx::smem_u32(order_slot), 1), v);
+    }
+    if constexpr (CTAS == 2) {
+      ptx::cluster_arrive_release();
+      ptx::cluster_wait_acquire();
+    } else {
+      __syncthreads();
+    }
+    cluster = *reinterpret_cast<volatile uint32_t*>(order_slot);
   }
 
   const uint32_t k_blocks = p.k_blocks;
@@ -1395,6 +1470,16 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
+  }
+  if (p.die_tickets != nullptr && rank == 0 && threadIdx.x == 0) {
+    // Every pair drew its ticket before it did anything else, so when the last one leaves nobody
+    // needs the counters any more.
+    if (atomicAdd(p.die_tickets + 2, 1u) == num_clusters - 1u) {
+      p.die_tickets[0] = 0u;
+      p.die_tickets[1] = 0u;
+      p.die_tickets[2] = 0u;
+      __threadfence();
+    }
   }
   if constexpr (PROF) {
     if (p.prof && threadIdx.x == 32) p.prof[16 * blockIdx.x + 15] = clock64() - kernel_t0;

@@ -106,6 +106,12 @@ typedef enum gz_config {
  * park fp32 partial sums in a workspace owned by the plan; the last CTA to arrive adds them in K
  * order.  Chosen automatically when it balances the SMs better; these flags override the choice.
  * A plan that uses the workspace must not run concurrently with itself on two streams. */
+/* Large problems on a two-die part: by default the plan measures once per device which die each SM
+ * sits on and lets the CTAs of one die take neighbouring tiles of each wave (less die-to-die
+ * traffic).  Results do not depend on it.  The order keeps 32 small sets of counters per plan, one
+ * per launch in flight; a caller that keeps MORE than 32 launches of one plan in flight at the
+ * same time on different streams must switch it off. */
+#define GZ_FLAG_NO_DIE_ORDER 0x40u
 #define GZ_FLAG_NO_SPLIT_K 0x4u
 #define GZ_FLAG_SPLIT_K 0x8u
 /* Test knob: the MMA warp never signals "accumulator ready", so the epilogue's
@@ -151,6 +157,8 @@ typedef struct gz_plan_info {
   int64_t tiles;        /* output tiles */
   int64_t workspace_bytes; /* device scratch memory owned by the plan */
   int64_t lda, ldb, ldc, ldd;
+  int32_t die_order;    /* 1 if the die-aware tile order is on (see GZ_FLAG_NO_DIE_ORDER) */
+  int32_t reserved2;
 } gz_plan_info;
 
 /* Host-only validation of a descriptor: every argument error is reachable
@@ -170,6 +178,15 @@ GZ_API gz_status gz_gemm_plan_info(const gz_plan* plan, gz_plan_info* info);
  * family (GZ_CFG_1CTA_N64, GZ_CFG_2CTA_N256, GZ_CFG_2CTA_M512_N256, GZ_CFG_SWAP_M16); other plans
  * return GZ_ERR_UNSUPPORTED.  No counterpart in the reference. */
 GZ_API gz_status gz_gemm_plan_set_profile(gz_plan* plan, void* device_words);
+
+/* Diagnostics of the die-aware tile order (no counterpart in the reference, which predates
+ * two-die parts).  gz_device_placement: die (0 or 1) of every SM of `device` as the library
+ * measured it (die_of_sm: one byte per SM, at least 160 bytes), and the SMs per die;
+ * GZ_ERR_UNSUPPORTED when the device did not show two dies.  gz_classify_dies is the host-only
+ * half of that measurement: clocks[sm * lines + j] is what a load of probe line j cost from SM sm. */
+GZ_API gz_status gz_device_placement(int32_t device, uint8_t* die_of_sm, int32_t sms_on_die[2]);
+GZ_API gz_status gz_classify_dies(const uint32_t* clocks, int32_t sms, int32_t lines, uint8_t* die_of_sm,
+                                  int32_t sms_on_die[2]);
 
 /* Asynchronous on `stream` (a cudaStream_t passed as void*; NULL = legacy default stream).
  * a, b, c, d: device pointers.  c may be NULL when *beta == 0. */
