@@ -11,9 +11,11 @@ column-major, alpha = 1, beta = 0, seeded N(0,1) / N(0,1) * K^-1/2 operands gene
 by gz_fill.  Three operand sets (384 MiB each, larger than the 126 MB L2) are rotated so that no
 step finds its inputs in L2.  With N > 1 GPUs every rank runs the same slab on its own GPU (global
 problem M = K = 8192, N = 8192 * N_gpus, B sharded by column blocks, A replicated, no collective on
-the data path: weak scaling).  The timed region of K steps is repeated `--repeats` times, each
-bracketed by a barrier and a device synchronisation; `value` is the median repeat (max over ranks),
-and the spread is reported beside the SM clock sampled during each repeat.
+the data path: weak scaling).  The timed region of K steps is measured `--repeats` times, each
+bracketed by a barrier and a device synchronisation and each after a short idle pause and three
+untimed steps, so that every repeat is the same measurement (K steps from a cool chip); `value` is
+the median repeat (max over ranks), and the spread is reported beside the SM clock sampled during
+each repeat.  What the chip sustains once the power limit sets the clock is the `sustained` leg.
 
 Keys beyond the base contract:
   roofline            tensor-bound: achieved = 2MNK / mean kernel time of the median repeat (CUDA
@@ -376,6 +378,29 @@ def e2e_leg(cx, gemm, A0, B0, steps):
     ms, _, _ = timed_region(cx, run, steps)
     ms_max = cx.max_over_ranks([ms])[0]
     d2h = M * N * 2
+    # What the bus alone needs for one step's bytes: the same host buffers copied up and down at the
+    # same time on two streams, no GEMM, all ranks at once.  The leg above cannot be faster than this.
+    up = torch.empty(h2d // 2, dtype=bf16, device=cx.dev)
+    down = torch.empty(M, N, dtype=bf16, device=cx.dev)
+    s_up, s_down = torch.cuda.Stream(cx.dev), torch.cuda.Stream(cx.dev)
+    flat_a, flat_b = ha.view(-1), hb.view(-1)
+    na = h2d // 2 - flat_b.numel()
+
+    def bus_only(_):
+        s_up.wait_stream(cx.stream)
+        s_down.wait_stream(cx.stream)
+        with torch.cuda.stream(s_up):
+            up[:na].copy_(flat_a[:na], non_blocking=True)
+            up[na:].copy_(flat_b, non_blocking=True)
+        with torch.cuda.stream(s_down):
+            hd.copy_(down, non_blocking=True)
+        cx.stream.wait_stream(s_up)
+        cx.stream.wait_stream(s_down)
+
+    bus_only(0)
+    bus_ms, _, _ = timed_region(cx, bus_only, steps)
+    bus_ms_max = cx.max_over_ranks([bus_ms])[0]
+    run(0)  # leave the product in hd again for the caller's comparison
     flops = 2.0 * M * N * K
     # the result the host now holds is the product: compare a few entries with the device-resident run
     checksum = float(hd[:4, :4].float().abs().sum())
@@ -384,6 +409,9 @@ def e2e_leg(cx, gemm, A0, B0, steps):
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_max / steps, "steps": steps,
             "rank0_h2d_gbs": h2d / per_rank_ms / 1e6, "rank0_d2h_gbs": d2h / per_rank_ms / 1e6,
             "aggregate_pcie_gbs": cx.world * (h2d + d2h) / (ms_max / steps) / 1e6,
+            "bus_only": {"ms_per_step": bus_ms_max / steps, "aggregate_gbs": cx.world * (h2d + d2h) / (bus_ms_max / steps) / 1e6,
+                         "what": "the step's host-to-device and device-to-host bytes copied concurrently, no GEMM, all ranks at once"},
+            "fraction_of_bus_only": (bus_ms_max / steps) / (ms_max / steps),
             "path": how, "result_checksum": checksum, "host_memory": "pinned, first touched on the GPU's NUMA node"}, hd
 
 
@@ -655,6 +683,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--repeats", type=int, default=10, help="how many times the timed region of --steps steps is measured")
+    ap.add_argument("--cooldown", type=float, default=0.3, help="idle seconds between repeats")
+    ap.add_argument("--no-die-order", action="store_true",
+                    help="headline plan without the die-aware tile order (for before/after counter captures)")
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-extras", action="store_true",
                     help="headline leg, partitioned leg and end-to-end leg only (same as --extras none)")
@@ -700,7 +731,8 @@ def main():
         # A is replicated across ranks (same seed); each rank owns its own column block of B.
         gz.fill(A[i], 1000 + i, 1, 1, 1.0)
         gz.fill(B[i], 2000 + i, 2 + rank, 1, K ** -0.5)
-    gemm = gz.Sm100Gemm(M, N, K, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR, device=local_rank)
+    gemm = gz.Sm100Gemm(M, N, K, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR, device=local_rank,
+                        flags=gz.FLAG_NO_DIE_ORDER if args.no_die_order else 0)
     info = gemm.info()
     flops = 2.0 * M * N * K
 
@@ -713,7 +745,15 @@ def main():
     cx.barrier()
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
-    regions = [timed_region(cx, step, args.steps) for _ in range(max(1, args.repeats))]
+    regions = []
+    for r in range(max(1, args.repeats)):
+        if r:
+            # Every repeat measures the same thing as the first: K steps on a chip that was idle just
+            # before (the seconds-long loop further down measures the power-capped regime).
+            time.sleep(args.cooldown)
+            for i in range(3):
+                step(i)
+        regions.append(timed_region(cx, step, args.steps))
     t_head_end = time.perf_counter()
     status, detail = gemm.plan.device_status(stream)
     if status != 0:
@@ -749,7 +789,8 @@ def main():
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": config_dict(world),
         "kernel": {"config": info.config, "tile": [info.tile_m, info.tile_n, info.tile_k], "stages": info.stages,
-                   "ctas_per_tile": info.ctas_per_tile, "grid": info.grid, "epilogue_tma": info.epilogue_tma},
+                   "ctas_per_tile": info.ctas_per_tile, "grid": info.grid, "epilogue_tma": info.epilogue_tma,
+                   "die_order": info.die_order},
         "repeats": repeats,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                      "frac": achieved / peak_tf,

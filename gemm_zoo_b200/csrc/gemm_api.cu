@@ -894,6 +894,11 @@ struct ScatterSpec {
   int parts;
   int64_t ld;
   void* ptrs[8];
+  // completion signal raised by the launch's last CTA (see GemmParams::signal_count); 0 = none
+  int signal_count = 0;
+  uint32_t signal_value = 0;
+  uint32_t* signal_ptrs[8] = {};
+  uint32_t* signal_counter = nullptr;
 };
 
 gz_status run_impl(gz_plan* pl, const void* a, const void* b, const void* c, void* d, const void* alpha,
@@ -996,6 +1001,12 @@ gz_status run_impl(gz_plan* pl, const void* a, const void* b, const void* c, voi
       if (i < sc->parts && reinterpret_cast<uintptr_t>(sc->ptrs[i]) % 16 != 0) vec = false;
     }
     p.d_vec_ok = vec ? 1u : 0u;
+    if (sc->signal_count > 0 && sc->signal_counter) {
+      p.signal_count = (uint32_t)sc->signal_count;
+      p.signal_value = sc->signal_value;
+      p.signal_counter = sc->signal_counter;
+      for (int i = 0; i < 8; ++i) p.signal_ptrs[i] = i < sc->signal_count ? sc->signal_ptrs[i] : nullptr;
+    }
   }
 
   if (pl->die_tickets)
@@ -1179,11 +1190,12 @@ gz_status run_host_impl(gz_plan* pl, const void* a, const void* b, const void* c
   }
   const int64_t cols = pl->block_cols;
   const size_t isz = pr.in_size, osz = pr.out_size;
-  // With a host A the uploads start where the caller's stream stands.  With a resident A the
-  // caller's stream may still be waiting for A to be gathered; the uploads of B must not wait for
-  // that too (the previous call returned with both copy streams idle, so nothing else orders them).
+  // The uploads start where the caller's stream stands.  With a resident A that is after whatever
+  // the caller queued to make A valid (its own slice's upload and the gather): the slice gets the
+  // host-to-device direction of the link to itself first, because nothing can be multiplied before
+  // A is complete, and the blocks of B follow.
   bool ok = cuda_ok(cudaEventRecord(pl->ev_start, stream), "cudaEventRecord") &&
-            (a_on_device || cuda_ok(cudaStreamWaitEvent(pl->copy_in, pl->ev_start, 0), "cudaStreamWaitEvent")) &&
+            cuda_ok(cudaStreamWaitEvent(pl->copy_in, pl->ev_start, 0), "cudaStreamWaitEvent") &&
             cuda_ok(cudaStreamWaitEvent(pl->copy_out, pl->ev_start, 0), "cudaStreamWaitEvent") &&
             (a_on_device || cuda_ok(cudaMemcpyAsync(pl->ha, a, a_bytes, cudaMemcpyHostToDevice, pl->copy_in), "H2D A"));
   for (int j = 0; ok && j < pl->blocks; ++j) {

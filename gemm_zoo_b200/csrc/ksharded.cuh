@@ -5,7 +5,8 @@
 // Workspace of one rank (the owner of one column block), identical on every rank:
 //   slots [2 sets][world][m][cols] 4-byte partial sums   (cols = n / world)
 //   flags [2 sets][GZ_KS_MAX_WORLD] uint32                (flag[set][g] = epoch of rank g's last push)
-// Rank g writes slot [set][g] of EVERY rank's workspace during its GEMM and then flag [set][g];
+// Rank g writes slot [set][g] of EVERY rank's workspace during its GEMM; the last CTA of that GEMM
+// to leave then writes flag [set][g] of every rank (GemmParams::signal_count: no second launch);
 // the owner reads all of its slots once all of its flags show the current epoch.
 #ifndef GZ_KSHARDED_CUH
 #define GZ_KSHARDED_CUH
@@ -33,19 +34,6 @@ KsLayout ks_layout(int64_t m, int64_t cols, int world) {
   return l;
 }
 
-struct KsFlagTargets {
-  uint32_t* ptr[GZ_KS_MAX_WORLD];
-};
-
-// After this rank's GEMM has completed (stream order), tell every owner that its slot is written.
-__global__ void ks_signal_kernel(KsFlagTargets targets, int world, uint32_t epoch) {
-  const int g = threadIdx.x;
-  if (g < world) {
-    __threadfence_system();
-    *reinterpret_cast<volatile uint32_t*>(targets.ptr[g]) = epoch;
-    __threadfence_system();
-  }
-}
 
 template <typename TOut>
 struct KsOut;
@@ -277,8 +265,9 @@ GZ_API gz_status gz_ks_plan_create(gz_ks_plan** out, const gz_ks_desc* desc, voi
   }
   pl->sm_count = pl->gemm->info.sm_count;
   DeviceGuard guard(desc->device);
-  if (!guard.ok() || !cuda_ok(cudaMalloc(&pl->status, 4 * sizeof(uint32_t)), "cudaMalloc(status)") ||
-      !cuda_ok(cudaMemset(pl->status, 0, 4 * sizeof(uint32_t)), "cudaMemset(status)")) {
+  // four status words and the arrival counter of the completion signal
+  if (!guard.ok() || !cuda_ok(cudaMalloc(&pl->status, 8 * sizeof(uint32_t)), "cudaMalloc(status)") ||
+      !cuda_ok(cudaMemset(pl->status, 0, 8 * sizeof(uint32_t)), "cudaMemset(status)")) {
     if (pl->status) cudaFree(pl->status);
     gz_gemm_plan_destroy(pl->gemm);
     delete pl;
@@ -307,15 +296,17 @@ GZ_API gz_status gz_ks_push(gz_ks_plan* pl, const void* a, const void* b, void* 
   sc.cols = (uint32_t)pl->cols;
   sc.parts = pl->d.world;
   sc.ld = pl->cols;
-  KsFlagTargets targets;
+  sc.signal_count = pl->d.world;
+  sc.signal_value = epoch;
+  sc.signal_counter = pl->status + 4;  // the word after the four status words
   for (int g = 0; g < GZ_KS_MAX_WORLD; ++g) {
     sc.ptrs[g] = nullptr;
-    targets.ptr[g] = nullptr;
+    sc.signal_ptrs[g] = nullptr;
     if (g >= pl->d.world) continue;
     char* base = static_cast<char*>(pl->ws[g]);
-    // my slot in owner g's set
+    // my slot in owner g's set, and my flag there
     sc.ptrs[g] = base + (set * pl->layout.set_elems + (size_t)pl->d.rank * pl->layout.slot_elems) * 4;
-    targets.ptr[g] = reinterpret_cast<uint32_t*>(base + pl->layout.flags_off) + set * GZ_KS_MAX_WORLD + pl->d.rank;
+    sc.signal_ptrs[g] = reinterpret_cast<uint32_t*>(base + pl->layout.flags_off) + set * GZ_KS_MAX_WORLD + pl->d.rank;
   }
   const float one_f = 1.0f, zero_f = 0.0f;
   const int32_t one_i = 1, zero_i = 0;
@@ -323,8 +314,6 @@ GZ_API gz_status gz_ks_push(gz_ks_plan* pl, const void* a, const void* b, void* 
   gz_status st = run_impl(pl->gemm, a, b, nullptr, sc.ptrs[pl->d.rank], s8 ? (const void*)&one_i : (const void*)&one_f,
                           s8 ? (const void*)&zero_i : (const void*)&zero_f, stream_v, &sc);
   if (st != GZ_OK) return st;
-  ks_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_v)>>>(targets, pl->d.world, epoch);
-  if (!cuda_ok(cudaGetLastError(), "flag kernel launch")) return GZ_ERR_CUDA;
   pl->epoch = epoch;
   return GZ_OK;
 }

@@ -118,6 +118,13 @@ struct GemmParams {
   // partial sums straight to the GPU that owns the block.  Direct-store epilogue only.
   uint32_t scatter_cols;
   void* scatter_ptrs[8];
+  // Completion signal (signal_count == 0: off).  The CTA that leaves the kernel last, after every
+  // CTA's output stores have been fenced system-wide, writes signal_value to signal_ptrs[0 ..
+  // signal_count): the K-sharded GEMM tells every owner "my partial sums are in your memory" from
+  // inside the GEMM instead of from a second launch.  signal_counter: one word, zero between launches.
+  uint32_t signal_count, signal_value;
+  uint32_t* signal_ptrs[8];
+  uint32_t* signal_counter;
   // Optional epilogue terms (floating-point outputs only), applied in fp32:
   //   D = act(alpha * row_scale[i] * col_scale[j] * acc + beta * C + bias[j])
   // epi_flags != 0 says that at least one of them is present (bit 0 bias, 1 row_scale,
@@ -362,10 +369,26 @@ __device__ __forceinline__ float acc_as_float(uint32_t v) {
   else return __uint_as_float(v);
 }
 
+// erf to about 2e-7 absolute (Abramowitz & Stegun 7.1.26: 1 - (a1 t + ... + a5 t^5) exp(-z^2),
+// t = 1 / (1 + p z), |error| <= 1.5e-7 before rounding) in a dozen instructions.  GELU multiplies it
+// by x / 2, and erf is exactly +-1 in fp32 beyond |z| = 4, so the activation stays well inside fp32
+// accuracy; the library erff costs about three times as many instructions, and this runs once per
+// output element in the epilogue of the last tile, which nothing overlaps.
+__device__ __forceinline__ float erf_fast(float z) {
+  const float az = fabsf(z);
+  const float t = __frcp_rn(fmaf(0.3275911f, az, 1.0f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float e = __expf(-az * az);
+  return copysignf(fmaf(-poly * t, e, 1.0f), z);
+}
+
 __device__ __forceinline__ float activate(float x, uint32_t act) {
   switch (act) {
     case 1: return fmaxf(x, 0.0f);
-    case 2: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    case 2: return 0.5f * x * (1.0f + erf_fast(x * 0.70710678118654752f));
     case 3: {
       const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
       return 0.5f * x * (1.0f + tanhf(u));
@@ -1470,6 +1493,17 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
+  }
+  if (p.signal_count != 0u && threadIdx.x == 0) {
+    // The barriers above ordered this CTA's output stores before this thread; the fence makes
+    // them visible to the other GPUs before the arrival is counted.
+    __threadfence_system();
+    if (atomicAdd(p.signal_counter, 1u) == gridDim.x - 1u) {
+      *p.signal_counter = 0u;
+      __threadfence_system();
+      for (uint32_t g = 0; g < p.signal_count; ++g) *reinterpret_cast<volatile uint32_t*>(p.signal_ptrs[g]) = p.signal_value;
+      __threadfence_system();
+    }
   }
   if (p.die_tickets != nullptr && rank == 0 && threadIdx.x == 0) {
     // Every pair drew its ticket before it did anything else, so when the last one leaves nobody

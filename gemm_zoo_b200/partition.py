@@ -9,8 +9,8 @@ nvidia/utils/benchmark.cuh:20); this is the multi-GPU form of the same call.
 `PartitionedHostGemm`  operands in HOST memory.  A replicated operand must not cross the host's
                        PCIe fabric once per GPU: rank g uploads only rows `row_slice(M, G, g)` of A
                        over its own link and the slices are all-gathered GPU to GPU (NCCL over
-                       NVLink) into every GPU's LOCAL copy of A, while this rank's column blocks of
-                       B are already streaming up; the kernels read local memory only.  Per rank and
+                       NVLink) into every GPU's LOCAL copy of A; then this rank's column blocks
+                       of B stream up; the kernels read local memory only.  Per rank and
                        call the bus carries |A|/G + |B shard| up and |D shard| down.
 
 `pin_near_gpu` allocates pinned host memory on the NUMA node the GPU hangs off, so that its DMA
@@ -124,8 +124,8 @@ class PartitionedHostGemm(PartitionedGemm):
             if hi > lo:
                 self.a_dev[lo:hi].copy_(a_host[lo:hi], non_blocking=True)
             gather_rows(self.a_dev, self.m, self.world, self.rank, self.group)
-        # The GEMMs of the column blocks wait for A on `stream`; the uploads of B start at once on
-        # the plan's own copy stream.
+        # Everything below is ordered after A on `stream`: the slice had the upload direction of the
+        # link to itself, the gather ran over NVLink, and now the blocks of B follow.
         stream.wait_stream(self.side)
         self.gemm.plan.run_host(self.a_dev, b_host_shard, c_host_shard, d_host_shard, alpha, beta, stream,
                                 a_on_device=True)

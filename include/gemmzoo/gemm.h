@@ -236,9 +236,9 @@ GZ_API gz_status gz_gemm_run_host(gz_plan* plan, const void* a, const void* b, c
  * counterpart there).  With GZ_HOST_A_ON_DEVICE, `a` is a DEVICE pointer on the plan's GPU whose
  * contents are valid in the order of `stream`: the replicated operand, of which every GPU uploaded
  * only a slice and which was then gathered GPU to GPU, instead of crossing the host's PCIe fabric
- * once per GPU.  b, c, d stay host pointers.  The uploads of B start at once on the plan's copy
- * stream (they do not wait for work already queued on `stream`, such as that gather); the GEMMs
- * run on `stream`, after it.  host_flags == 0 is gz_gemm_run_host. */
+ * once per GPU.  b, c, d stay host pointers.  Everything the call does is ordered after the work
+ * already queued on `stream` (the slice's upload and the gather): the slice has the link to itself
+ * first, the blocks of B follow.  host_flags == 0 is gz_gemm_run_host. */
 #define GZ_HOST_A_ON_DEVICE 0x1u
 GZ_API gz_status gz_gemm_run_host_ex(gz_plan* plan, const void* a, const void* b, const void* c, void* d,
                                      const void* alpha, const void* beta, void* stream, uint32_t host_flags);

@@ -8,7 +8,7 @@
  * over N.  Instead of computing a full partial and then calling a collective, the
  * GEMM's epilogue stores every column block of its fp32 (int32 for s8) partial sums straight into
  * the memory of the GPU that owns the block (plain peer stores over NVLink, tile by tile while the
- * main loop runs); a one-warp kernel then raises a flag on every peer, and the owner's reduce kernel
+ * main loop runs); the CTA of that GEMM that finishes last raises a flag on every peer, and the owner's reduce kernel
  * waits (bounded) for the world's flags, adds the slots in rank order (deterministic), applies
  * alpha/beta and casts.  Two sets of slots alternate, so a rank may start its next GEMM while a
  * slower peer still reduces the previous one.

@@ -50,7 +50,7 @@ def test_resident_a_host_b_matches_device_operands(m, n, k):
     """gz_gemm_run_host_ex with GZ_HOST_A_ON_DEVICE: A already sits in the GPU's memory (the
     replicated operand of a column-partitioned run), B, C and D are host memory; the result equals
     the device-operand run bit for bit, also when A only becomes valid through work queued on the
-    caller's stream just before the call (the uploads of B do not wait for it, the GEMMs do)."""
+    caller's stream just before the call (the call's own work is ordered after it)."""
     gen = torch.Generator().manual_seed(m)
     a = torch.randn(m, k, generator=gen).bfloat16().pin_memory()
     b = (torch.randn(n, k, generator=gen) * k ** -0.5).bfloat16().pin_memory()
