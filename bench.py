@@ -34,6 +34,8 @@ Keys beyond the base contract:
   configs             every benchmark configuration of the specification on one GPU, own kernel
                       beside cuBLASLt (device time per launch from CUDA-graph replays), each with its
                       roofline
+  fused_epilogue      bf16 2048 x 14336 x 4096 with bias + GELU in the epilogue beside the plain GEMM
+  timeline            where the time of a short launch goes (the kernel's own global-timer stamps)
   cublaslt            cuBLASLt on the headline operands in the same process, interleaved
   cpu_baseline        the CPU restatement of the reference's naive GEMM (oracle/), OpenMP over all
                       host cores, timed on a bounded row sample of the headline workload
@@ -194,7 +196,7 @@ def cpu_reference_tflops(rows, threads=None):
     if "b" not in _CPU_DATA:
         rng = np.random.default_rng(1)
         # bf16 bit patterns of N(0,1) and N(0,1)/sqrt(K): top 16 bits of the fp32 values.
-        _CPU_DATA["a"] = (rng.standard_normal((2048, K), dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        _CPU_DATA["a"] = (rng.standard_normal((M, K), dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
         _CPU_DATA["b"] = ((rng.standard_normal((N, K), dtype=np.float32) * K ** -0.5).view(np.uint32) >> 16).astype(np.uint16)
         orc.gemm_f64(orc.DT_BF16, orc.DT_BF16, _CPU_DATA["a"][:8], _CPU_DATA["b"], None, 8, N, K, b_col_major=True)
     a, b = _CPU_DATA["a"][:rows], _CPU_DATA["b"]
@@ -628,6 +630,85 @@ def fused_epilogue_leg(cx, reps=20):
             "bias_gelu_us": round(t_fused, 2), "fused_over_plain_time": round(t_fused / t_plain, 3)}
 
 
+def timeline_leg(cx):
+    """Where the time of a short launch goes.  Six launches of one problem back to back in one CUDA
+    graph, each plan with the kernel's built-in timeline switched on (gz_gemm_plan_set_profile:
+    global-timer stamps per CTA); reported per phase in microseconds, medians over launches 2..6:
+      release     last CTA of the previous launch left -> this launch may touch global memory
+                  (the launch itself and its set-up overlap the previous kernel: programmatic
+                  dependent launch)
+      first_data  -> the first operand stage has landed at the MMA warp (slowest CTA)
+      main_loop   -> the last MMA is issued
+      epilogue    -> the last output stores are issued
+      tail        -> the last CTA has left
+    The stamps cost a few clock reads per K block, so the sum runs a few percent above an
+    uninstrumented launch."""
+    torch, gz = cx.torch, cx.gz
+    stream = torch.cuda.Stream(cx.dev)
+    W = gz.PROFILE_WORDS_PER_CTA
+    out = {}
+    for name, (m, n, k, cfg) in {"bf16_1024_cubed": (1024, 1024, 1024, gz.CFG_1CTA_N64),
+                                 "bf16_m16_n14336_k4096": (16, 14336, 4096, gz.CFG_SWAP_M16),
+                                 "bf16_2048_cubed": (2048, 2048, 2048, gz.CFG_2CTA_N256)}.items():
+        L = 6
+        A = [torch.empty(m, k, dtype=torch.bfloat16, device=cx.dev) for _ in range(L)]
+        B = [torch.empty(n, k, dtype=torch.bfloat16, device=cx.dev) for _ in range(L)]
+        D = torch.empty(m, n, dtype=torch.bfloat16, device=cx.dev)
+        for i in range(L):
+            gz.fill(A[i], 9, 2 * i, 1, 1.0)
+            gz.fill(B[i], 9, 2 * i + 1, 1, k ** -0.5)
+        plans = [gz.Sm100Gemm(m, n, k, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR, config=cfg, device=cx.local_rank)
+                 for _ in range(L)]
+        grid = plans[0].info().grid
+        bufs = [torch.zeros(W * grid, dtype=torch.int64, device=cx.dev) for _ in range(L)]
+        for pl, b in zip(plans, bufs):
+            pl.plan.set_profile(b)
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                for i in range(L):
+                    plans[i](A[i], B[i], None, D, 1.0, 0.0, stream=stream)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(L):
+                    plans[i](A[i], B[i], None, D, 1.0, 0.0, stream=stream)
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+        ws = [b.cpu().view(grid, W)[:, 16:].double() for b in bufs]
+
+        def col(w, i, fn):
+            v = w[:, i]
+            v = v[v > 0]  # CTAs that do not play the role (the second CTA of a pair) leave zeros
+            return float(fn(v)) if len(v) else float("nan")
+
+        phases = {"release": [], "first_data": [], "main_loop": [], "epilogue": [], "tail": [], "launch_to_launch": []}
+        for i in range(1, L):
+            prev_exit = col(ws[i - 1], 7, max)
+            ready = col(ws[i], 1, max)
+            first = col(ws[i], 2, max)
+            mma_done = col(ws[i], 3, max)
+            stores = col(ws[i], 5, max)
+            exit_ = col(ws[i], 7, max)
+            phases["release"].append(ready - prev_exit)
+            phases["first_data"].append(first - ready)
+            phases["main_loop"].append(mma_done - first)
+            phases["epilogue"].append(stores - mma_done)
+            phases["tail"].append(exit_ - stores)
+            phases["launch_to_launch"].append(exit_ - prev_exit)
+        med = lambda v: round(sorted(v)[len(v) // 2] / 1e3, 2)
+        out[name] = {"kernel_config": cfg, "grid": grid, "us": {k2: med(v) for k2, v in phases.items()},
+                     "graph_us_per_launch": round(e0.elapsed_time(e1) * 1e3 / L, 2)}
+        for pl in plans:
+            pl.plan.destroy()
+        del A, B, D, bufs
+    return out
+
+
 def ksharded_leg(cx, reps=20):
     """K-sharded GEMM (rank g holds A[:, K_g], B[K_g, :]) with the reduce-scatter fused into the
     epilogue (peer stores over NVLink), beside the GEMM + NCCL reduce-scatter route; both routes
@@ -690,12 +771,12 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="headline leg, partitioned leg and end-to-end leg only (same as --extras none)")
     ap.add_argument("--extras", default="all",
-                    help="comma list of the optional legs: cublaslt,sustained,configs,fused,cpu,ksharded; all; none")
+                    help="comma list of the optional legs: cublaslt,sustained,configs,fused,timeline,cpu,ksharded; all; none")
     ap.add_argument("--sustain", type=float, default=2.0,
                     help="seconds each of the seconds-long own / cuBLASLt loops (0 = skip)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "own" else args.warmup
-    all_extras = {"cublaslt", "sustained", "configs", "fused", "cpu", "ksharded"}
+    all_extras = {"cublaslt", "sustained", "configs", "fused", "timeline", "cpu", "ksharded"}
     extras = set() if (args.no_extras or args.extras == "none") else (
         all_extras if args.extras == "all" else set(args.extras.split(",")) & all_extras)
 
@@ -839,8 +920,15 @@ def main():
                 line["fused_epilogue"] = fused_epilogue_leg(cx)
             except Exception as e:
                 line["fused_epilogue"] = {"error": repr(e)}
+        if "timeline" in extras:
+            try:
+                line["timeline"] = timeline_leg(cx)
+            except Exception as e:
+                line["timeline"] = {"error": repr(e)}
         if "cpu" in extras:
-            rows = 2048 if (os.cpu_count() or 1) >= 32 else 512
+            # a bounded sample of 10-20 s of CPU work: a 256-row probe sets the row count
+            tf0, _, _ = cpu_reference_tflops(256)
+            rows = int(max(256, min(M, 15.0 * tf0 * 1e12 / (2.0 * N * K)) // 256 * 256))
             tf, dt, cores = cpu_reference_tflops(rows)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                     "sample": f"{rows} of {M} rows of A (all columns, full K), {dt:.1f} s, fp64 accumulation"}

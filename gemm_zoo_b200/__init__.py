@@ -13,7 +13,7 @@ from .api import (  # noqa: F401
     COL_MAJOR, ROW_MAJOR, DT_BF16, DT_F16, DT_F32, DT_S8, DT_S32, DT_E4M3, DT_E5M2,
     FLAG_EPILOGUE_DIRECT, FLAG_EPILOGUE_TMA, FLAG_TEST_WITHHOLD_ACC_READY, FLAG_NO_SPLIT_K, FLAG_SPLIT_K, FLAG_BROADCAST_A, FLAG_BROADCAST_B,
     GemmDesc, GzError, Plan, PlanInfo, Sm100Gemm, fill, lib, lib_path, partition_columns,
-    status_string, tile_coords, validate, EXPORTED_SYMBOLS, gemm_skinny_static, static_device_status, classify_dies, device_placement, FLAG_NO_DIE_ORDER,
+    status_string, tile_coords, validate, EXPORTED_SYMBOLS, gemm_skinny_static, static_device_status, classify_dies, device_placement, FLAG_NO_DIE_ORDER, PROFILE_WORDS_PER_CTA,
     STATIC_SCRATCH_BYTES,
     ACT_NONE, ACT_RELU, ACT_GELU, ACT_GELU_TANH, ACT_SILU, Epilogue,
 )

@@ -20,6 +20,7 @@ FLAG_NO_SPLIT_K, FLAG_SPLIT_K = 0x4, 0x8
 FLAG_BROADCAST_A, FLAG_BROADCAST_B = 0x10, 0x20
 FLAG_NO_DIE_ORDER = 0x40
 HOST_A_ON_DEVICE = 0x1
+PROFILE_WORDS_PER_CTA = 24
 
 GZ_OK = 0
 GZ_ERR_INVALID_ARG, GZ_ERR_UNSUPPORTED, GZ_ERR_MISALIGNED, GZ_ERR_CUDA = 1, 2, 3, 4
@@ -286,11 +287,11 @@ class Plan:
             raise GzError(st, "gz_gemm_run_host")
 
     def set_profile(self, buf):
-        """buf: contiguous torch int64 CUDA tensor of at least 16 * info().grid words (the kernel
-        writes 16 words per CTA), or None to switch the counters off."""
+        """buf: contiguous torch int64 CUDA tensor of at least PROFILE_WORDS_PER_CTA * info().grid
+        words (the kernel writes that many per CTA), or None to switch the counters off."""
         if buf is not None:
             import torch
-            need = 16 * self.info().grid
+            need = PROFILE_WORDS_PER_CTA * self.info().grid
             if not (isinstance(buf, torch.Tensor) and buf.is_cuda and buf.dtype == torch.int64 and
                     buf.is_contiguous() and buf.numel() >= need):
                 raise ValueError(f"set_profile needs a contiguous int64 CUDA tensor of at least {need} words")

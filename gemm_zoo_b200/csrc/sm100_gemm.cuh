@@ -148,7 +148,7 @@ struct GemmParams {
   // between launches; two launches that overlap on the GPU must not share them.
   uint32_t* die_tickets;
   uint8_t die_of_sm[160];
-  // Optional stall counters, 16 words per CTA (null = off):
+  // Optional stall counters and timeline, PROF_WORDS = 24 words per CTA (null = off):
   //  [0] A producer: clocks waiting for a free stage   [1] A producer: total clocks
   //  [2] MMA: clocks waiting for operand data          [3] MMA: clocks waiting for a free accumulator
   //  [4] MMA: total clocks                             [5] epilogue warp 2: clocks waiting for an accumulator
@@ -159,9 +159,17 @@ struct GemmParams {
   //       accumulators to registers)
   //  [13] MMA: clocks waiting for the second accumulator of a two-row-block tile (part of [3])
   //  [14] clocks from kernel entry to the end of set-up   [15] clocks from kernel entry to exit
-  // Only kernels instantiated with PROF = true write them.
+  // Words 16..23 are a timeline in nanoseconds of the global timer (comparable between the CTAs of
+  // one launch and between consecutive launches):
+  //  [16] kernel entry                      [17] set-up done and dependencies of the launch satisfied
+  //  [18] MMA: first operand stage landed   [19] MMA: last MMA of the CTA's last tile issued
+  //  [20] epilogue warp 2: last accumulator ready   [21] its last output stores issued
+  //  [22] shared memory of those stores read out (TMA-store epilogue; else = [21])   [23] kernel exit
+  // Only kernels instantiated with PROF = true write them; the buffer holds PROF_WORDS words per CTA.
   unsigned long long* prof;
 };
+
+constexpr uint32_t PROF_WORDS = 24;
 
 enum : uint32_t {
   // Tiles start their K range at different K blocks and wrap around.  Set by the plan for skinny
@@ -677,6 +685,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   constexpr int BN = Cfg::BN;
 
   const long long kernel_t0 = PROF ? clock64() : 0;
+  const uint64_t tl_entry = PROF ? ptx::globaltimer_ns() : 0;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // 128B-swizzle atoms need 1024-byte alignment
@@ -757,7 +766,11 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   ptx::grid_launch_dependents();
   ptx::grid_dependency_wait();
   if constexpr (PROF) {
-    if (p.prof && threadIdx.x == 32) p.prof[16 * blockIdx.x + 14] = setup_clocks;
+    if (p.prof && threadIdx.x == 32) {
+      p.prof[PROF_WORDS * blockIdx.x + 14] = setup_clocks;
+      p.prof[PROF_WORDS * blockIdx.x + 16] = tl_entry;
+      p.prof[PROF_WORDS * blockIdx.x + 17] = ptx::globaltimer_ns();
+    }
   }
 
   // Which tiles this CTA (pair) takes: those of its hardware index, or, with the die-aware order,
@@ -851,9 +864,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
     if constexpr (PROF) {
       if (lane == 0 && p.prof) {
-        p.prof[16 * blockIdx.x + (is_b ? 10 : 0)] = prof_wait;
-        p.prof[16 * blockIdx.x + (is_b ? 11 : 8)] = prof_issue;
-        if (!is_b) p.prof[16 * blockIdx.x + 1] = clock64() - prof_t0;
+        p.prof[PROF_WORDS * blockIdx.x + (is_b ? 10 : 0)] = prof_wait;
+        p.prof[PROF_WORDS * blockIdx.x + (is_b ? 11 : 8)] = prof_issue;
+        if (!is_b) p.prof[PROF_WORDS * blockIdx.x + 1] = clock64() - prof_t0;
       }
     }
     if (!ok && rank == 0 && lane == 0) {
@@ -880,6 +893,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       long long prof_full = 0, prof_tmem = 0, prof_tmem1 = 0, prof_issue = 0;
       const long long prof_t0 = PROF ? clock64() : 0;
       const uint64_t prof_ns0 = PROF ? ptx::globaltimer_ns() : 0;
+      uint64_t tl_first = 0;
       const uint32_t a_hi = p.a.desc_hi, b_hi = p.b.desc_hi;
       const uint32_t a_lo0 = ((base >> 4) & 0x3FFFu) | p.a.desc_lo;
       const uint32_t b_lo0 = (((base + Cfg::A_BYTES) >> 4) & 0x3FFFu) | p.b.desc_lo;
@@ -927,7 +941,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             ok = __all_sync(0xFFFFFFFFu, got);
             if (!ok) break;
             const long long w2 = PROF ? clock64() : 0;
-            if constexpr (PROF) prof_full += w2 - w1;
+            if constexpr (PROF) {
+              prof_full += w2 - w1;
+              if (tl_first == 0) tl_first = ptx::globaltimer_ns();
+            }
             ptx::tc_fence_after_sync();
             if (ptx::elect_one()) issue_block(0, kb_lo + i, st);
             __syncwarp();
@@ -970,7 +987,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           ok = __all_sync(0xFFFFFFFFu, got);
           if (!ok) break;
           const long long w2 = PROF ? clock64() : 0;
-          if constexpr (PROF) prof_full += w2 - w1;
+          if constexpr (PROF) {
+            prof_full += w2 - w1;
+            if (tl_first == 0) tl_first = ptx::globaltimer_ns();
+          }
           ptx::tc_fence_after_sync();
           if (ptx::elect_one()) {
 #pragma unroll
@@ -1004,12 +1024,14 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
       if constexpr (PROF) {
         if (lane == 0 && p.prof) {
-          p.prof[16 * blockIdx.x + 2] = prof_full;
-          p.prof[16 * blockIdx.x + 3] = prof_tmem;
-          p.prof[16 * blockIdx.x + 4] = clock64() - prof_t0;
-          p.prof[16 * blockIdx.x + 7] = ptx::globaltimer_ns() - prof_ns0;
-          p.prof[16 * blockIdx.x + 9] = prof_issue;
-          p.prof[16 * blockIdx.x + 13] = prof_tmem1;
+          p.prof[PROF_WORDS * blockIdx.x + 2] = prof_full;
+          p.prof[PROF_WORDS * blockIdx.x + 3] = prof_tmem;
+          p.prof[PROF_WORDS * blockIdx.x + 4] = clock64() - prof_t0;
+          p.prof[PROF_WORDS * blockIdx.x + 7] = ptx::globaltimer_ns() - prof_ns0;
+          p.prof[PROF_WORDS * blockIdx.x + 9] = prof_issue;
+          p.prof[PROF_WORDS * blockIdx.x + 13] = prof_tmem1;
+          p.prof[PROF_WORDS * blockIdx.x + 18] = tl_first;
+          p.prof[PROF_WORDS * blockIdx.x + 19] = ptx::globaltimer_ns();
         }
       }
       if ((!ok || (p.test_flags & 1u)) && issued && lane == 0) {
@@ -1044,6 +1066,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       bool ok = true;
       const bool prof = PROF && p.prof != nullptr && warp == 2 && lane == 0;
       long long prof_wait = 0, prof_copy = 0;
+      uint64_t tl_acc = 0;
       const long long prof_t0 = prof ? clock64() : 0;
       const TOut* const cmat = static_cast<const TOut*>(p.c);
       const uint32_t tmem_empty_target =
@@ -1099,6 +1122,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               ok = false;
               break;
             }
+            if (prof) tl_acc = ptx::globaltimer_ns();
             ptx::tc_fence_after_sync();
 #pragma unroll
             for (int sl = 0; sl < NSL; ++sl) {
@@ -1166,7 +1190,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             break;
           }
           const long long c0 = prof ? clock64() : 0;
-          if (prof) prof_wait += c0 - w0;
+          if (prof) {
+            prof_wait += c0 - w0;
+            tl_acc = ptx::globaltimer_ns();
+          }
           ptx::tc_fence_after_sync();
           const uint32_t row0 = tm * (Cfg::BM * CTAS) + rank * Cfg::BM + mb * 128u + quad * 32u;
           const uint32_t row = row0 + lane;
@@ -1295,11 +1322,15 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
       // The CTA's shared memory must outlive the reads of its last TMA stores; the writes
       // themselves complete on their own before the grid does.
+      const uint64_t tl_issued = prof ? ptx::globaltimer_ns() : 0;
       if (p.epilogue_tma && lane == 0) ptx::bulk_wait_group_read<0>();
       if (prof) {
-        p.prof[16 * blockIdx.x + 5] = prof_wait;
-        p.prof[16 * blockIdx.x + 6] = clock64() - prof_t0;
-        p.prof[16 * blockIdx.x + 12] = prof_copy;
+        p.prof[PROF_WORDS * blockIdx.x + 5] = prof_wait;
+        p.prof[PROF_WORDS * blockIdx.x + 6] = clock64() - prof_t0;
+        p.prof[PROF_WORDS * blockIdx.x + 12] = prof_copy;
+        p.prof[PROF_WORDS * blockIdx.x + 20] = tl_acc;
+        p.prof[PROF_WORDS * blockIdx.x + 21] = tl_issued;
+        p.prof[PROF_WORDS * blockIdx.x + 22] = ptx::globaltimer_ns();
       }
     } else {
     const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32) are readable by this warp
@@ -1307,6 +1338,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     bool ok = true;
     const bool prof = PROF && p.prof != nullptr && warp == 2 && lane == 0;
     long long prof_wait = 0, prof_park = 0;
+    uint64_t tl_acc = 0;
     const long long prof_t0 = prof ? clock64() : 0;
     const TOut* const cmat = static_cast<const TOut*>(p.c);
     const uint32_t tmem_empty_target =
@@ -1323,7 +1355,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         ok = false;
         break;
       }
-      if (prof) prof_wait += clock64() - w0;
+      if (prof) {
+        prof_wait += clock64() - w0;
+        tl_acc = ptx::globaltimer_ns();
+      }
       ptx::tc_fence_after_sync();
       {
         // Swapped operands: accumulator lane = output column (n), accumulator column = output row (m).
@@ -1467,9 +1502,12 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       if (acc == 0u) acc_phase ^= 1u;
     }
     if (prof) {
-      p.prof[16 * blockIdx.x + 5] = prof_wait;
-      p.prof[16 * blockIdx.x + 6] = clock64() - prof_t0;
-      p.prof[16 * blockIdx.x + 12] = prof_park;
+      p.prof[PROF_WORDS * blockIdx.x + 5] = prof_wait;
+      p.prof[PROF_WORDS * blockIdx.x + 6] = clock64() - prof_t0;
+      p.prof[PROF_WORDS * blockIdx.x + 12] = prof_park;
+      p.prof[PROF_WORDS * blockIdx.x + 20] = tl_acc;
+      p.prof[PROF_WORDS * blockIdx.x + 21] = ptx::globaltimer_ns();
+      p.prof[PROF_WORDS * blockIdx.x + 22] = p.prof[PROF_WORDS * blockIdx.x + 21];
     }
     }
   }
@@ -1516,7 +1554,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
   }
   if constexpr (PROF) {
-    if (p.prof && threadIdx.x == 32) p.prof[16 * blockIdx.x + 15] = clock64() - kernel_t0;
+    if (p.prof && threadIdx.x == 32) {
+      p.prof[PROF_WORDS * blockIdx.x + 15] = clock64() - kernel_t0;
+      p.prof[PROF_WORDS * blockIdx.x + 23] = ptx::globaltimer_ns();
+    }
   }
 }
 

@@ -170,13 +170,16 @@ GZ_API gz_status gz_gemm_plan_create(gz_plan** plan, const gz_gemm_desc* desc);
 GZ_API gz_status gz_gemm_plan_destroy(gz_plan* plan);
 GZ_API gz_status gz_gemm_plan_info(const gz_plan* plan, gz_plan_info* info);
 
-/* Diagnostics: give the plan a device buffer of 16 * info.grid 64-bit words and
- * every later launch records, per CTA, the clocks its producer, MMA and epilogue
- * roles spent waiting (layout: see GemmParams::prof in csrc/sm100_gemm.cuh).
- * NULL switches it off again.  The buffer must hold at least 16 * info.grid words: nothing checks
- * a raw pointer's size.  Counters are compiled in for bf16 -> bf16 plans of one tile shape per
+/* Diagnostics: give the plan a device buffer of GZ_PROFILE_WORDS_PER_CTA * info.grid 64-bit words and
+ * every later launch records, per CTA, the clocks its producer, MMA and epilogue roles spent
+ * waiting (words 0..15) and a timeline in global-timer nanoseconds (words 16..23: entry, set-up
+ * done and dependencies satisfied, first operands landed, last MMA issued, last accumulator ready,
+ * last stores issued, their shared memory read out, exit); layout: GemmParams::prof in
+ * csrc/sm100_gemm.cuh.  NULL switches it off again.  The buffer must hold at least that many
+ * words: nothing checks a raw pointer's size.  Counters are compiled in for bf16 -> bf16 plans of one tile shape per
  * family (GZ_CFG_1CTA_N64, GZ_CFG_2CTA_N256, GZ_CFG_2CTA_M512_N256, GZ_CFG_SWAP_M16); other plans
  * return GZ_ERR_UNSUPPORTED.  No counterpart in the reference. */
+#define GZ_PROFILE_WORDS_PER_CTA 24
 GZ_API gz_status gz_gemm_plan_set_profile(gz_plan* plan, void* device_words);
 
 /* Diagnostics of the die-aware tile order (no counterpart in the reference, which predates
