@@ -25,6 +25,7 @@ PROFILE_WORDS_PER_CTA = 24
 GZ_OK = 0
 GZ_ERR_INVALID_ARG, GZ_ERR_UNSUPPORTED, GZ_ERR_MISALIGNED, GZ_ERR_CUDA = 1, 2, 3, 4
 GZ_ERR_DEVICE_TIMEOUT, GZ_ERR_NO_DEVICE, GZ_ERR_TOO_LARGE, GZ_ERR_OUT_OF_MEMORY = 5, 6, 7, 8
+GZ_ERR_DEBUG_CHECK = 9
 
 # Every symbol include/gemmzoo/gemm.h declares.
 EXPORTED_SYMBOLS = [
@@ -111,6 +112,12 @@ _lib = None
 
 def lib_path() -> Path:
     return PKG / "libgemmzoo.so"
+
+
+def debug_lib_path() -> Path:
+    """The same library compiled with -DGZ_BOUNDS_CHECK (bounds-checked epilogue stores); tests
+    load it by pointing `lib_path` at it in a process of their own."""
+    return PKG / "libgemmzoo_dbg.so"
 
 
 def lib():

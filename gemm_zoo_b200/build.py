@@ -6,6 +6,7 @@
 Targets
   lib        gemm_zoo_b200/libgemmzoo.so        the C ABI + sm_100a kernels (one object per
                                                  translation unit, compiled in parallel)
+  debug      gemm_zoo_b200/libgemmzoo_dbg.so    the same with bounds-checked epilogue stores
   cublaslt   gemm_zoo_b200/libgz_cublaslt.so    cuBLASLt comparator (bench/tests only)
   bench      gemm_zoo_b200/nvidia/bench/build/* bench mains built against the C++ functor
 
@@ -59,10 +60,12 @@ def lib_sources():
     return [CSRC / "gemm_api.cu"] + sorted((CSRC / "inst").glob("*.cu"))
 
 
-def build_lib(force=False, verbose=False, ptxas_info=False, jobs=None) -> Path:
-    out = PKG / "libgemmzoo.so"
+def build_lib(force=False, verbose=False, ptxas_info=False, jobs=None, debug=False) -> Path:
+    """debug=True: libgemmzoo_dbg.so, the same sources with -DGZ_BOUNDS_CHECK (every plain global
+    store of the epilogue checks its coordinates first); used by tests/test_debug_bounds.py."""
+    out = PKG / ("libgemmzoo_dbg.so" if debug else "libgemmzoo.so")
     headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list((INCLUDE / "gemmzoo").glob("*.h"))
-    objdir = CSRC / "build"
+    objdir = CSRC / ("build_dbg" if debug else "build")
     objdir.mkdir(exist_ok=True)
     todo, objs = [], []
     for src in lib_sources():
@@ -71,6 +74,8 @@ def build_lib(force=False, verbose=False, ptxas_info=False, jobs=None) -> Path:
         if force or _newer(obj, [src] + headers):
             cmd = [nvcc_path(), *ARCH, *NVCC_COMMON, "-Xcompiler", "-fPIC,-fvisibility=hidden", "-c",
                    f"-I{INCLUDE}", f"-I{CSRC}", "-o", obj, src]
+            if debug:
+                cmd += ["-DGZ_BOUNDS_CHECK"]
             if ptxas_info:
                 cmd += ["-Xptxas", "-v"]
             todo.append(cmd)
@@ -114,7 +119,7 @@ def build_bench(force=False, verbose=False):
 
 
 def build_all(force=False, verbose=False):
-    res = {"lib": build_lib(force, verbose)}
+    res = {"lib": build_lib(force, verbose), "lib_debug": build_lib(force, verbose, debug=True)}
     if (PKG / "cmp" / "cublaslt_cmp.cu").exists():
         res["cublaslt"] = build_cublaslt(force, verbose)
     if list((PKG / "nvidia" / "bench").glob("*.cu")):
@@ -131,6 +136,8 @@ if __name__ == "__main__":
             print(build_all(force, True))
         elif w == "lib":
             print(build_lib(force, True, ptxas_info=True))
+        elif w == "debug":
+            print(build_lib(force, True, debug=True))
         elif w == "cublaslt":
             print(build_cublaslt(force, True))
         elif w == "bench":

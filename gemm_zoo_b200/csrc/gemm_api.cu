@@ -625,6 +625,7 @@ GZ_API const char* gz_status_string(gz_status s) {
     case GZ_ERR_NO_DEVICE: return "no CUDA device of compute capability 10.x";
     case GZ_ERR_TOO_LARGE: return "extent too large";
     case GZ_ERR_OUT_OF_MEMORY: return "out of memory";
+    case GZ_ERR_DEBUG_CHECK: return "debug build: an epilogue store failed its bounds check and was skipped";
   }
   return "unknown status";
 }
@@ -1277,7 +1278,7 @@ GZ_API gz_status gz_last_device_status(gz_plan* pl, void* stream_v, uint32_t det
       const size_t counter_bytes = (size_t)pl->base.grid.num_tiles * (size_t)pl->pr.d.batch * 4;
       (void)cudaMemset(pl->base.counters, 0, counter_bytes);
     }
-    return GZ_ERR_DEVICE_TIMEOUT;
+    return h[0] == gz::STORE_OUT_OF_BOUNDS ? GZ_ERR_DEBUG_CHECK : GZ_ERR_DEVICE_TIMEOUT;
   }
   return GZ_OK;
 }
@@ -1567,7 +1568,7 @@ extern "C" GZ_API gz_status gz_static_last_device_status(int32_t device, void* s
   if (detail) std::memcpy(detail, h, sizeof(h));
   if (h[0] != 0) {
     (void)cudaMemset(words, 0, sizeof(h));
-    return GZ_ERR_DEVICE_TIMEOUT;
+    return h[0] == gz::STORE_OUT_OF_BOUNDS ? GZ_ERR_DEBUG_CHECK : GZ_ERR_DEVICE_TIMEOUT;
   }
   return GZ_OK;
 }

@@ -78,6 +78,9 @@ enum WaitCode : uint32_t {
   WAIT_EPILOGUE_TMEM_FULL = 4,
   WAIT_MMA_DRAIN = 5
 };
+// Written to status[0] by a debug build (GZ_BOUNDS_CHECK) when an epilogue store would have left
+// the output matrix; status[1] = block, status[2] = row, status[3] = column of the refused store.
+constexpr uint32_t STORE_OUT_OF_BOUNDS = 32;
 
 struct GemmParams {
   OperandDesc a, b;
@@ -418,6 +421,28 @@ __device__ __forceinline__ float epi_finish(const GemmParams& p, float f, uint32
   return activate(f, p.act);
 }
 
+// Debug builds (compiled with -DGZ_BOUNDS_CHECK) check every plain global store of the epilogue
+// before it is made: the coordinates must lie inside the output matrix (rows x cols of this
+// problem of the batch).  A store that fails the check is recorded and skipped, never made; TMA
+// stores need no check, the hardware clips them to the tensor map.  Release builds compile the
+// check away.
+#if defined(GZ_BOUNDS_CHECK)
+static __device__ __noinline__ bool store_in_bounds(const GemmParams& p, uint32_t row, uint32_t col, uint32_t ncols,
+                                                    uint32_t rows, uint32_t cols) {
+  if (row < rows && col < cols && ncols <= cols - col) return true;
+  if (atomicCAS(p.status, 0u, STORE_OUT_OF_BOUNDS) == 0u) {
+    p.status[1] = blockIdx.x;
+    p.status[2] = row;
+    p.status[3] = col;
+    __threadfence();
+  }
+  return false;
+}
+#define GZ_STORE_OK(p, row, col, ncols, rows, cols) detail::store_in_bounds(p, row, col, ncols, rows, cols)
+#else
+#define GZ_STORE_OK(p, row, col, ncols, rows, cols) true
+#endif
+
 // alpha * acc + beta * c for one 32-column slice of one row.
 //   v[32]     in:  raw accumulator words;  out: packed output words (32 * sizeof(TOut) / 4 used)
 //   crow      pointer to C(row, col0) (only dereferenced when beta != 0 and row_ok)
@@ -607,7 +632,8 @@ __device__ __forceinline__ void store_staged_box(const GemmParams& p, uint32_t s
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "r"(stg + r * 128u + ((j ^ (r & 7u)) << 4))
                  : "memory");
-    if (row0 + r < p.m) *reinterpret_cast<uint4*>(out_ptr<TOut>(p, row0 + r, box_col + j * PER16, batch)) = v;
+    if (row0 + r < p.m && GZ_STORE_OK(p, row0 + r, box_col + j * PER16, PER16, p.m, p.n))
+      *reinterpret_cast<uint4*>(out_ptr<TOut>(p, row0 + r, box_col + j * PER16, batch)) = v;
   }
 }
 
@@ -1290,7 +1316,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     }
                   } else if (row_ok) {
                     TOut* drow = detail::out_ptr<TOut>(p, row, col0, bidx);
-                    detail::store_direct<TOut>(x, drow, ncols, p.d_vec_ok != 0u);
+                    if (GZ_STORE_OK(p, row, col0, ncols, p.m, p.n))
+                      detail::store_direct<TOut>(x, drow, ncols, p.d_vec_ok != 0u);
                   }
                 }
                 if (p.epilogue_tma) {
@@ -1387,6 +1414,14 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           const uint32_t last = detail::split_owner(tile_u0 + k_blocks - 1u, p.total_kb, num_clusters);
           contributors = last - first + 1u;
           my_slot = cluster - first;
+#if defined(GZ_BOUNDS_CHECK)
+          // the workspace holds max_contrib slots per tile (rows = slots, cols = tiles of the launch)
+          if (!detail::store_in_bounds(p, my_slot, t, 1u, p.max_contrib, static_cast<uint32_t>(p.total_kb / k_blocks))) {
+            *reinterpret_cast<volatile uint32_t*>(ab.flag) = 1u;  // every role of the CTA gives up
+            ok = false;
+            break;
+          }
+#endif
           float4* slot = reinterpret_cast<float4*>(p.ws) +
                          (static_cast<size_t>(t) * p.max_contrib + my_slot) * SLOT_F4 + lane_off;
 #pragma unroll
@@ -1476,14 +1511,14 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               if (has_beta) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
-                  if (static_cast<uint32_t>(i) < cnt)
+                  if (static_cast<uint32_t>(i) < cnt && GZ_STORE_OK(p, mrow0 + i, ncol, 1u, p.n, p.m))
                     dp[static_cast<int64_t>(i) * p.ldd] =
                         detail::epilogue_scalar<TOut, true, ACC_INT>(v[i], p, cp + static_cast<int64_t>(i) * p.ldc,
                                                                      mrow0 + i, ncol);
               } else {
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
-                  if (static_cast<uint32_t>(i) < cnt)
+                  if (static_cast<uint32_t>(i) < cnt && GZ_STORE_OK(p, mrow0 + i, ncol, 1u, p.n, p.m))
                     dp[static_cast<int64_t>(i) * p.ldd] =
                         detail::epilogue_scalar<TOut, false, ACC_INT>(v[i], p, nullptr, mrow0 + i, ncol);
               }

@@ -59,7 +59,8 @@ typedef enum gz_status {
   GZ_ERR_DEVICE_TIMEOUT = 5, /* a bounded wait inside the kernel expired */
   GZ_ERR_NO_DEVICE = 6,      /* no CUDA device, or device is not compute capability 10.x */
   GZ_ERR_TOO_LARGE = 7,      /* extent exceeds what the kernel's 32-bit tile coordinates hold */
-  GZ_ERR_OUT_OF_MEMORY = 8
+  GZ_ERR_OUT_OF_MEMORY = 8,
+  GZ_ERR_DEBUG_CHECK = 9     /* debug build only (libgemmzoo_dbg.so): an epilogue store failed its bounds check */
 } gz_status;
 
 typedef enum gz_dtype {
@@ -284,7 +285,11 @@ GZ_API gz_status gz_static_last_device_status(int32_t device, void* stream, uint
 /* Synchronises the plan's device status word: returns GZ_OK, or
  * GZ_ERR_DEVICE_TIMEOUT if a bounded wait expired in any launch since the last
  * call (detail[0] = role/barrier code, detail[1] = block, detail[2] = tile,
- * detail[3] = k-block; may be NULL).  Blocks until `stream` is idle. */
+ * detail[3] = k-block; may be NULL).  Blocks until `stream` is idle.
+ * The debug build of the library (libgemmzoo_dbg.so, compiled with -DGZ_BOUNDS_CHECK: every plain
+ * global store of the epilogue checks its coordinates against the output matrix first, and a
+ * store that fails is skipped) reports GZ_ERR_DEBUG_CHECK here, with detail = {32, block, row,
+ * column} of the first refused store. */
 GZ_API gz_status gz_last_device_status(gz_plan* plan, void* stream, uint32_t detail[4]);
 
 GZ_API const char* gz_status_string(gz_status s);
