@@ -1159,7 +1159,9 @@ gz_status run_host_impl(gz_plan* pl, const void* a, const void* b, const void* c
   {
     std::lock_guard<std::mutex> lock(pl->mu);
     if (!pl->pipe_ready) {
-      int64_t cols = cdiv(cdiv(pr.d.n, 8), 256) * 256;  // about 8 blocks, 256-column granularity
+      // About 16 blocks, 256-column granularity: what nothing can overlap is the last block's GEMM
+      // and download, so the blocks are as small as the event budget (kMaxBlocks) allows.
+      int64_t cols = cdiv(cdiv(pr.d.n, gz_plan::kMaxBlocks), 256) * 256;
       if (cols < 256) cols = 256;
       int blocks = (int)cdiv(pr.d.n, cols);
       if (blocks > gz_plan::kMaxBlocks) {
