@@ -639,6 +639,7 @@ def timeline_leg(cx):
                   dependent launch)
       first_data  -> the first operand stage has landed at the MMA warp (slowest CTA)
       main_loop   -> the last MMA is issued
+      acc_ready   -> the last accumulator is complete and the epilogue warps have woken
       epilogue    -> the last output stores are issued
       tail        -> the last CTA has left
     The stamps cost a few clock reads per K block, so the sum runs a few percent above an
@@ -686,18 +687,21 @@ def timeline_leg(cx):
             v = v[v > 0]  # CTAs that do not play the role (the second CTA of a pair) leave zeros
             return float(fn(v)) if len(v) else float("nan")
 
-        phases = {"release": [], "first_data": [], "main_loop": [], "epilogue": [], "tail": [], "launch_to_launch": []}
+        phases = {"release": [], "first_data": [], "main_loop": [], "acc_ready": [], "epilogue": [], "tail": [],
+                  "launch_to_launch": []}
         for i in range(1, L):
             prev_exit = col(ws[i - 1], 7, max)
             ready = col(ws[i], 1, max)
             first = col(ws[i], 2, max)
             mma_done = col(ws[i], 3, max)
+            acc = col(ws[i], 4, max)
             stores = col(ws[i], 5, max)
             exit_ = col(ws[i], 7, max)
             phases["release"].append(ready - prev_exit)
             phases["first_data"].append(first - ready)
             phases["main_loop"].append(mma_done - first)
-            phases["epilogue"].append(stores - mma_done)
+            phases["acc_ready"].append(acc - mma_done)
+            phases["epilogue"].append(stores - acc)
             phases["tail"].append(exit_ - stores)
             phases["launch_to_launch"].append(exit_ - prev_exit)
         med = lambda v: round(sorted(v)[len(v) // 2] / 1e3, 2)
