@@ -1106,6 +1106,13 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const TOut* const cmat_b = cmat + static_cast<int64_t>(bidx) * p.stride_c;
         const uint32_t wcols = work.cols / HALVES;  // columns of this piece that belong to this warp
         const uint32_t col_w = tn * BN + work.col_off + half * wcols;
+        // Warm the address translation of this warp's part of the output while the main loop runs
+        // (see the swapped epilogue): one prefetch per warp, first row and first column it will store.
+        if (lane == 0) {
+          const uint32_t pf_row = tm * (Cfg::BM * CTAS) + rank * Cfg::BM + quad * 32u;
+          if (pf_row < p.m && col_w < p.n && p.scatter_cols == 0u)  // never a peer GPU's memory
+            ptx::prefetch_l2(detail::out_ptr<TOut>(p, pf_row, col_w, bidx));
+        }
         if constexpr (Cfg::MB == 2 && sizeof(TOut) == 2) {
           // 16-bit outputs without a C term: a warp's share of BOTH accumulators fits in its
           // registers once packed (2 x 64 words), so both accumulators go back to the MMA warp
@@ -1377,6 +1384,16 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint32_t bidx = t / p.grid.num_tiles;  // problem of the batch
       tile_coords(p.grid, t - bidx * p.grid.num_tiles, tm, tn);
       const TOut* const cmat_b = cmat + static_cast<int64_t>(bidx) * p.stride_c;
+      // The first store to a page the SM has not touched waits about a microsecond for its address
+      // translation, and in a skinny problem the output is first touched after the last MMA, where
+      // nothing hides that.  So the output rows of the tile are touched now, while the main loop
+      // runs: one prefetch per row, by the first lanes of the warp that will store there.
+      {
+        const uint32_t pf_col = tm * 128u + quad * 32u;
+        const uint32_t pf_row = tn * BN + lane;
+        if (lane < static_cast<uint32_t>(BN) && pf_col < p.m && pf_row < p.n && p.scatter_cols == 0u)
+          ptx::prefetch_l2(detail::out_ptr<TOut>(p, pf_row, pf_col, bidx));
+      }
       const long long w0 = prof ? clock64() : 0;
       if (!detail::wait(tmem_full_bar(acc), acc_phase, ab, WAIT_EPILOGUE_TMEM_FULL, t, 0)) {
         ok = false;
