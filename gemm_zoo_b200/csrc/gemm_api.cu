@@ -474,7 +474,13 @@ const gz::DevicePlacement* placement_of(int device, int sm_count) {
   if (device < 0 || device >= 64) return nullptr;
   std::lock_guard<std::mutex> lock(g_placement_mu);
   if (!g_placement_done[device]) {
-    g_placement[device] = gz::measure_placement(sm_count);  // the device is current (plan creation)
+    // The device is current (plan creation).  The probe times L2 hits, so a measurement taken while
+    // the clocks ramp up from idle can be too noisy to classify: try a few times before giving up
+    // (giving up only switches the die-aware order off).
+    for (int attempt = 0; attempt < 4; ++attempt) {
+      g_placement[device] = gz::measure_placement(sm_count);
+      if (g_placement[device].known) break;
+    }
     g_placement_done[device] = true;
   }
   return &g_placement[device];

@@ -153,6 +153,9 @@ inline DevicePlacement measure_placement(int sm_count) {
       }
     }
     if (ok) out.known = classify_dies(by_sm, sm_count, kLines, out.die_of_sm, out.sms_on_die);
+    // The two SMs of a TPC (2t, 2t + 1) sit side by side: a picture that splits one is noise.
+    for (int s = 0; out.known && s + 1 < sm_count; s += 2)
+      if (out.die_of_sm[s] != out.die_of_sm[s + 1]) out.known = false;
   }
   (void)cudaGetLastError();
   if (stream) cudaStreamDestroy(stream);

@@ -787,17 +787,15 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const long long setup_clocks = PROF ? clock64() - kernel_t0 : 0;
 
   // Everything above touched only this CTA's shared and tensor memory and the kernel's parameters,
-  // so it may overlap the tail of the previous kernel of the stream; from here on global memory is
-  // read and written.  The next kernel may start its own set-up as soon as SMs come free.
+  // so it may overlap the tail of the previous kernel of the stream.  The next kernel may start
+  // its own set-up as soon as SMs come free.
   ptx::grid_launch_dependents();
-  ptx::grid_dependency_wait();
-  if constexpr (PROF) {
-    if (p.prof && threadIdx.x == 32) {
-      p.prof[PROF_WORDS * blockIdx.x + 14] = setup_clocks;
-      p.prof[PROF_WORDS * blockIdx.x + 16] = tl_entry;
-      p.prof[PROF_WORDS * blockIdx.x + 17] = ptx::globaltimer_ns();
-    }
-  }
+  // Each role waits for the launch's dependencies itself, as late as it can: the producers after
+  // they have worked out their first piece (index arithmetic and parameter reads, which miss the
+  // constant cache in a fresh launch, then overlap the previous kernel's tail), the epilogue warps
+  // before their first access to C or D; the MMA warp touches no global memory.  The ticket draw
+  // of the die-aware order is a global-memory access, so such launches wait here.
+  if (p.die_tickets != nullptr) ptx::grid_dependency_wait();
 
   // Which tiles this CTA (pair) takes: those of its hardware index, or, with the die-aware order,
   // those of the number it draws now (see GemmParams::die_tickets).
@@ -838,6 +836,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const uint32_t bk = p.bk;
     uint32_t stage = 0, phase = 0;
     bool ok = true;
+    bool dep_waited = false;
     long long prof_wait = 0, prof_issue = 0;
     const long long prof_t0 = PROF ? clock64() : 0;
     detail::WorkIter work(p, cluster, num_clusters, BN);
@@ -851,6 +850,17 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                                 : static_cast<int32_t>(tm * (Cfg::BM * CTAS) + rank * Cfg::BM);
       const uint32_t nkb = kb_hi - kb_lo;
       const uint32_t rot = (p.tune & TUNE_K_STAGGER) ? (t * 31u) % nkb : 0u;
+      if (!dep_waited) {
+        ptx::grid_dependency_wait();
+        dep_waited = true;
+        if constexpr (PROF) {
+          if (p.prof && !is_b && lane == 0) {
+            p.prof[PROF_WORDS * blockIdx.x + 14] = setup_clocks;
+            p.prof[PROF_WORDS * blockIdx.x + 16] = tl_entry;
+            p.prof[PROF_WORDS * blockIdx.x + 17] = ptx::globaltimer_ns();
+          }
+        }
+      }
       for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
         const long long w0 = PROF ? clock64() : 0;
         const bool got = detail::wait(empty_bar(stage), phase ^ 1u, ab, WAIT_PRODUCER_EMPTY, t, kb);
@@ -1071,6 +1081,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
   } else {
     // ---------------------------------------------------------- epilogue
+    ptx::grid_dependency_wait();  // before the first access to C, D, the epilogue vectors or the split-K workspace
     if constexpr (!Cfg::SWAP) {
       // Four or eight warps; a warp reads the TMEM lanes of its quadrant (warp % 4) and, with
       // eight, one half of the tile's columns.  A warp first copies its whole share of an
@@ -1568,6 +1579,10 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   __syncwarp();
   ptx::tc_fence_before_sync();
   __syncthreads();
+  // Every thread passes the dependency wait before it leaves (a CTA without work has not yet; for
+  // the others it is satisfied): this grid then never completes before the one it follows, and
+  // the counters touched below are safe to touch.
+  ptx::grid_dependency_wait();
   if (detail::aborted(ab)) {
     // Loads issued by a peer CTA's producer are counted on the leader's
     // barriers; give anything still in flight time to land.
