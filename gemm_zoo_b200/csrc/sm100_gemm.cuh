@@ -576,6 +576,36 @@ __device__ __forceinline__ TOut epilogue_scalar(uint32_t acc, const GemmParams& 
   }
 }
 
+// The plain output path of a swapped tile (no C term, no epilogue vectors, floating-point output):
+// accumulator lane = output column, accumulator column = output row; row i of the tile goes to
+// dp + i * ldd.  Deliberately NOT inlined: the epilogue runs once per tile, long after anything
+// else the warp executed, so it runs at the speed instructions can be fetched; the caller runs
+// this once with store = false while it waits for its first accumulator (the loads read whatever
+// tensor memory holds and nothing is stored), which leaves the code in the instruction caches.
+template <typename TOut, int BN, bool ACC_INT>
+__device__ __noinline__ void swapped_store_plain(uint32_t taddr, TOut* dp, long long ldd, uint32_t rows, float alpha,
+                                                 bool store) {
+#pragma unroll
+  for (int sl = 0; sl < BN / 16; ++sl) {
+    if (static_cast<uint32_t>(sl * 16) >= rows) break;
+    uint32_t v[16];
+    ptx::tmem_ld_32x16(taddr + sl * 16u, v);
+    ptx::tmem_wait_ld();
+    const uint32_t cnt = (rows - sl * 16u < 16u) ? (rows - sl * 16u) : 16u;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (static_cast<uint32_t>(i) >= cnt) break;  // uniform
+      const float f = alpha * acc_as_float<ACC_INT>(v[i]);
+      if (store) {
+        TOut* const q = dp + static_cast<long long>(sl * 16 + i) * ldd;
+        if constexpr (sizeof(TOut) == 4) *q = f;
+        else if constexpr (std::is_same<TOut, __half>::value) *q = __float2half_rn(f);
+        else *q = __float2bfloat16_rn(f);
+      }
+    }
+  }
+}
+
 // Store one packed 32-column slice of one row straight to global memory.
 template <typename TOut>
 __device__ __forceinline__ void store_direct(const uint32_t (&v)[32], TOut* drow, uint32_t ncols,
@@ -1388,6 +1418,26 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const TOut* const cmat = static_cast<const TOut*>(p.c);
     const uint32_t tmem_empty_target =
         (CTAS == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+    // The plain output path (floating-point output, no C term, no epilogue vectors, no scatter, whole
+    // tiles) reads its parameters now and keeps them in registers: after the long wait for the
+    // accumulator every parameter read would miss the constant cache again, one after the other,
+    // with nothing left to hide it.
+    float alpha_r = p.alpha_f;
+    TOut* d_r = static_cast<TOut*>(p.d);
+    long long ldd_r = p.ldd, sd_r = p.stride_d;
+    uint32_t n_r = p.n, m_r = p.m;
+#if defined(GZ_BOUNDS_CHECK)
+    uint32_t fast_r = 0u;  // the checked build keeps every store on the path that checks its coordinates
+#else
+    uint32_t fast_r = (!detail::OutTraits<TOut>::INT && p.epi_flags == 0u && p.scatter_cols == 0u && p.beta_f == 0.0f) ? 1u : 0u;
+#endif
+    asm volatile("" : "+f"(alpha_r), "+l"(d_r), "+l"(ldd_r), "+l"(sd_r), "+r"(n_r), "+r"(m_r), "+r"(fast_r));
+    if constexpr (!detail::OutTraits<TOut>::INT) {
+      // Dry run of the output code (see swapped_store_plain): nothing is stored.
+      if (fast_r != 0u)
+        detail::swapped_store_plain<TOut, BN, ACC_INT>(tmem_base + ((quad * 32u) << 16), d_r, ldd_r,
+                                                       static_cast<uint32_t>(BN), alpha_r, false);
+    }
     detail::WorkIter work(p, cluster, num_clusters, BN);
     uint32_t t = 0, kb_lo = 0, kb_hi = 0;
     while (ok && work.next(t, kb_lo, kb_hi)) {
@@ -1476,6 +1526,17 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
         const long long e1 = prof ? clock64() : 0;
         if (prof) prof_park += e1 - e0;
+        if constexpr (!detail::OutTraits<TOut>::INT) {
+          if (finish && !partial && fast_r != 0u) {
+            const uint32_t mrow0 = tn * BN;
+            if (ncol0 < m_r && mrow0 < n_r) {
+              TOut* dp = d_r + static_cast<long long>(bidx) * sd_r + static_cast<long long>(mrow0) * ldd_r + ncol;
+              const uint32_t rows = (n_r - mrow0 < static_cast<uint32_t>(BN)) ? n_r - mrow0 : static_cast<uint32_t>(BN);
+              detail::swapped_store_plain<TOut, BN, ACC_INT>(taddr, dp, ldd_r, rows, alpha_r, ncol < m_r);
+            }
+            finish = false;  // the tile is written
+          }
+        }
         if (finish && ncol0 < p.m) {
           const bool has_beta = detail::OutTraits<TOut>::INT ? (p.beta_i != 0) : (p.beta_f != 0.0f);
 #pragma unroll
