@@ -849,6 +849,12 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   }
 
   const uint32_t k_blocks = p.k_blocks;
+  // What the teardown has to do besides freeing tensor memory, read now and kept in a register:
+  // the teardown runs once, at the very end, where every parameter read is a constant-cache miss
+  // that nothing overlaps.  Bit 0: completion signal, bit 1: die tickets, bit 2: timeline.
+  uint32_t late_work = (p.signal_count != 0u ? 1u : 0u) | (p.die_tickets != nullptr ? 2u : 0u) |
+                       ((PROF && p.prof != nullptr) ? 4u : 0u);
+  asm volatile("" : "+r"(late_work));
 
   if (warp == 0 || warp == 6) {
     // ---------------------------------------------------------- TMA producers
@@ -1660,7 +1666,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
   }
-  if (p.signal_count != 0u && threadIdx.x == 0) {
+  if ((late_work & 1u) && threadIdx.x == 0) {
     // The barriers above ordered this CTA's output stores before this thread; the fence makes
     // them visible to the other GPUs before the arrival is counted.
     __threadfence_system();
@@ -1671,7 +1677,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       __threadfence_system();
     }
   }
-  if (p.die_tickets != nullptr && rank == 0 && threadIdx.x == 0) {
+  if ((late_work & 2u) && rank == 0 && threadIdx.x == 0) {
     // Every pair drew its ticket before it did anything else, so when the last one leaves nobody
     // needs the counters any more.
     if (atomicAdd(p.die_tickets + 2, 1u) == num_clusters - 1u) {
@@ -1682,7 +1688,7 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
   }
   if constexpr (PROF) {
-    if (p.prof && threadIdx.x == 32) {
+    if ((late_work & 4u) && threadIdx.x == 32) {
       p.prof[PROF_WORDS * blockIdx.x + 15] = clock64() - kernel_t0;
       p.prof[PROF_WORDS * blockIdx.x + 23] = ptx::globaltimer_ns();
     }
