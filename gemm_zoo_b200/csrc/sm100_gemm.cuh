@@ -823,8 +823,8 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   // Each role waits for the launch's dependencies itself, as late as it can: the producers after
   // they have worked out their first piece (index arithmetic and parameter reads, which miss the
   // constant cache in a fresh launch, then overlap the previous kernel's tail), the epilogue warps
-  // before their first access to C or D; the MMA warp touches no global memory.  The ticket draw
-  // of the die-aware order is a global-memory access, so such launches wait here.
+  // before their first access to C or D, the MMA warp before its first bounded wait.  The ticket
+  // draw of the die-aware order is a global-memory access, so such launches wait here.
   if (p.die_tickets != nullptr) ptx::grid_dependency_wait();
 
   // Which tiles this CTA (pair) takes: those of its hardware index, or, with the die-aware order,
@@ -958,6 +958,9 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // ---------------------------------------------------------- MMA issuer
     // Only the leader CTA of a pair issues.  As in the producer, the whole warp
     // walks the loop and one elected lane issues tcgen05.mma / tcgen05.commit.
+    // The warp touches no global memory, but its bounded waits must not count the time the
+    // launch spends waiting for the kernel before it; no operand can land before that anyway.
+    ptx::grid_dependency_wait();
     if (rank == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;

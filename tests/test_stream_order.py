@@ -133,3 +133,39 @@ def test_accumulating_into_the_output_of_the_launch_before():
         g(a, b, d, d, 1.0, 1.0)
     torch.cuda.synchronize()
     assert torch.equal(d, once * steps)
+
+
+@pytest.mark.gpu
+def test_time_spent_waiting_for_the_previous_kernel_does_not_count_against_the_wait_limit():
+    """A launch whose CTAs are resident early (idle SMs, the kernel before it has signalled that
+    dependents may start) sits out the rest of that kernel inside `griddepcontrol.wait`; its bounded
+    waits start only afterwards, so a small wait limit does not turn a long predecessor into a
+    timeout."""
+    k_long = 1 << 22
+    slow = gz.Sm100Gemm(128, 128, k_long, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR, config=gz.CFG_1CTA_N128)
+    assert slow.info().grid == 1  # one CTA walks 65536 K blocks: about 15 ms, 147 SMs idle
+    a = torch.zeros(128, k_long, dtype=torch.bfloat16, device=DEV)
+    b = torch.zeros(128, k_long, dtype=torch.bfloat16, device=DEV)
+    d_slow = torch.empty(128, 128, dtype=torch.bfloat16, device=DEV)
+    m, n, k = 1024, 1024, 256
+    quick = gz.Sm100Gemm(m, n, k, gz.DT_BF16, gz.DT_BF16, layout_b=gz.COL_MAJOR, wait_limit_ns=1_000_000)
+    x = torch.empty(m, k, dtype=torch.bfloat16, device=DEV)
+    w = torch.empty(n, k, dtype=torch.bfloat16, device=DEV)
+    gz.fill(x, 31, 1, 1, 1.0)
+    gz.fill(w, 31, 2, 1, k ** -0.5)
+    want = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    quick(x, w, None, want, 1.0, 0.0)
+    slow(a, b, None, d_slow, 1.0, 0.0)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    got = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    e0.record()
+    slow(a, b, None, d_slow, 1.0, 0.0)
+    quick(x, w, None, got, 1.0, 0.0)  # directly behind: an event record in between would end the overlap
+    e1.record()
+    torch.cuda.synchronize()
+    if e0.elapsed_time(e1) < 2.0:
+        pytest.skip("the long kernel finished within twice the wait limit: nothing to show")
+    st, detail = quick.plan.device_status()
+    assert st == 0, (st, detail)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
