@@ -670,8 +670,14 @@ __device__ __forceinline__ void store_staged_box(const GemmParams& p, uint32_t s
 // alpha * acc (+ beta * c) for one full 32-column slice of one row, in place and without a second
 // register array: on return x[0 .. 32 * sizeof(TOut) / 4) holds the packed outputs.  `crow` points
 // at C(row, col0), 16-byte aligned; it is read only when HAS_BETA.
-template <typename TOut, bool HAS_BETA, bool ACC_INT>
-__device__ __forceinline__ void scale_slice_in_place(uint32_t (&x)[32], const GemmParams& p, const TOut* crow) {
+// The four scalars of the epilogue, for code that must not drag the whole parameter block along.
+struct EpiScalars {
+  float alpha_f, beta_f;
+  int32_t alpha_i, beta_i;
+};
+
+template <typename TOut, bool HAS_BETA, bool ACC_INT, class P>
+__device__ __forceinline__ void scale_slice_in_place(uint32_t (&x)[32], const P& p, const TOut* crow) {
   using Tr = OutTraits<TOut>;
   const uint4* c4 = reinterpret_cast<const uint4*>(crow);
   if constexpr (Tr::INT) {
@@ -724,6 +730,58 @@ __device__ __forceinline__ void scale_slice_in_place(uint32_t (&x)[32], const Ge
         }
         x[4 * q + e] = pack2<TOut>(lo, hi);
       }
+    }
+  }
+}
+
+// The plain epilogue of one warp's share of a tile (no C term, no epilogue vectors, whole share
+// inside the matrix, TMA store): copy NSL 32-column slices of the accumulator to registers, hand
+// the accumulator back (arrive on `empty_bar`), then scale, pack, stage and store box by box.
+// Not inlined, for the reason given at swapped_store_plain: a CTA with a single tile executes its
+// epilogue exactly once, cold, with nothing to overlap it; the caller runs this once with
+// live = false (no arrival, no store; it reads whatever tensor memory holds and writes only the
+// warp's own staging box) before it waits for its first accumulator.
+template <typename TOut, bool ACC_INT, int NSL, int CTAS>
+__device__ __noinline__ void plain_tile_epilogue(uint32_t taddr, uint32_t stg, const void* tmap_d, int32_t col_w,
+                                                 int32_t row0, int32_t bidx, EpiScalars sc, uint32_t empty_bar,
+                                                 bool live) {
+  constexpr int BOX_COLS = 128 / sizeof(TOut);
+  constexpr int SLICES = BOX_COLS / 32;
+  constexpr int WORDS = 32 * sizeof(TOut) / 4;
+  const uint32_t lane = threadIdx.x & 31u;
+  uint32_t v[NSL][32];
+#pragma unroll
+  for (int sl = 0; sl < NSL; ++sl) ptx::tmem_ld_32x32(taddr + sl * 32u, v[sl]);
+  ptx::tmem_wait_ld();
+  ptx::tc_fence_before_sync();
+  __syncwarp();
+  if (live && lane == 0) {
+    if constexpr (CTAS == 2) ptx::mbar_arrive_cluster(empty_bar);
+    else ptx::mbar_arrive(empty_bar);
+  }
+#pragma unroll
+  for (int box = 0; box < NSL / SLICES; ++box) {
+    // One staging box per warp: the store issued from it must have read it out.
+    if (lane == 0) ptx::bulk_wait_group_read<0>();
+    __syncwarp();
+#pragma unroll
+    for (int sl = 0; sl < SLICES; ++sl) {
+      uint32_t(&x)[32] = v[box * SLICES + sl];
+      scale_slice_in_place<TOut, false, ACC_INT>(x, sc, static_cast<const TOut*>(nullptr));
+#pragma unroll
+      for (int q = 0; q < WORDS / 4; ++q) {
+        const uint32_t j = static_cast<uint32_t>(sl * (WORDS / 4) + q);
+        const uint32_t addr = stg + lane * 128u + ((j ^ (lane & 7u)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x[4 * q]), "r"(x[4 * q + 1]),
+                     "r"(x[4 * q + 2]), "r"(x[4 * q + 3])
+                     : "memory");
+      }
+    }
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (live && lane == 0) {
+      ptx::tma_store_3d(tmap_d, stg, col_w + box * BOX_COLS, row0, bidx);
+      ptx::bulk_commit_group();
     }
   }
 }
@@ -1147,6 +1205,16 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const TOut* const cmat = static_cast<const TOut*>(p.c);
       const uint32_t tmem_empty_target =
           (CTAS == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+      // The plain path (see plain_tile_epilogue): its scalars are read now, and the routine runs
+      // once dry while there is nothing else to do.
+      const detail::EpiScalars sc{p.alpha_f, p.beta_f, p.alpha_i, p.beta_i};
+      const bool plain_tma = Cfg::MB == 1 && p.epilogue_tma != 0u && p.epi_flags == 0u &&
+                             (detail::OutTraits<TOut>::INT ? (p.beta_i == 0) : (p.beta_f == 0.0f));
+      if constexpr (Cfg::MB == 1) {
+        if (plain_tma)
+          detail::plain_tile_epilogue<TOut, ACC_INT, NSL, CTAS>(tmem_base + ((quad * 32u) << 16) + half * WARP_COLS, stg, &tm_d, 0,
+                                                                0, 0, sc, 0u, false);
+      }
       detail::WorkIter work(p, cluster, num_clusters, BN);
       uint32_t t = 0, kb_lo = 0, kb_hi = 0;
       while (ok && work.next(t, kb_lo, kb_hi)) {
@@ -1288,7 +1356,12 @@ sm100_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           // operands) takes the slice-by-slice path below, which frees the accumulator last.
           const bool fast = wcols == static_cast<uint32_t>(WARP_COLS) && col_w + WARP_COLS <= p.n &&
                             (p.epilogue_tma || p.d_vec_ok) && (!has_beta || p.c_vec_ok) && p.epi_flags == 0u;
-          if (fast) {
+          if (Cfg::MB == 1 && fast && plain_tma && row0 + 32u <= p.m) {
+            detail::plain_tile_epilogue<TOut, ACC_INT, NSL, CTAS>(taddr, stg, &tm_d, static_cast<int32_t>(col_w),
+                                                                  static_cast<int32_t>(row0), static_cast<int32_t>(bidx), sc,
+                                                                  tmem_empty_target + 8u * ai, true);
+            if (prof) prof_copy += clock64() - c0;
+          } else if (fast) {
             uint32_t v[NSL][32];
 #pragma unroll
             for (int sl = 0; sl < NSL; ++sl) ptx::tmem_ld_32x32(taddr + sl * 32u, v[sl]);
